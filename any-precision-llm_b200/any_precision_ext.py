@@ -27,8 +27,10 @@ import os
 
 import torch
 
+import warnings
+
 __all__ = ["matmul_kbit", "dequant_kbit", "gemm_kbit", "gemm_kbit_supported", "take_wait_expired", "library_path",
-           "load_library"]
+           "load_library", "reserve_workspace"]
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "lib", "libanyprec_sm100.so")
@@ -203,17 +205,49 @@ def _workspace(lib, device: torch.device, stream: int, M: int, N: int, splits: i
     return _workspace_bytes(device, stream, lib.ap_matmul_kbit_workspace_bytes(M, N, splits))
 
 
+_retired_workspaces: list = []     # superseded scratch tensors: captured graphs may still hold their addresses
+_warned_unsplit = False
+_MIN_WORKSPACE = 8 << 20            # covers 8 rows x 8 ranges x 28672 output rows (7.1 MB) without regrowing
+
+
 def _workspace_bytes(device: torch.device, stream: int, need: int):
     """The split-K scratch of (device, stream), grown to ``need`` bytes; its ticket area is zero between
-    calls.  None during a graph capture that would have to allocate (the caller then runs unsplit)."""
+    calls.  None during a graph capture that would have to allocate (the caller then runs unsplit, and
+    a warning says so once: call ``reserve_workspace`` before capturing).  A scratch tensor that was
+    handed out is never freed: a CUDA graph captured earlier holds its address as partial-sum and
+    ticket area, so when a larger one replaces it the old one is kept alive beside it."""
+    global _warned_unsplit
     key = (device.index, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
         if torch.cuda.is_current_stream_capturing():
+            if not _warned_unsplit:
+                _warned_unsplit = True
+                warnings.warn("any_precision_ext: the split-K scratch of this stream would have to grow during a CUDA "
+                              f"graph capture ({need} bytes needed); this call runs without split-K (slower on layers "
+                              "with few rows).  Call any_precision_ext.reserve_workspace(device, nbytes) on the "
+                              "capturing stream before the capture.", RuntimeWarning, stacklevel=3)
             return None                      # no allocation inside a graph capture: run unsplit
-        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            _retired_workspaces.append(ws)
+        ws = torch.zeros(max(need, _MIN_WORKSPACE), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def reserve_workspace(device=None, nbytes: int = _MIN_WORKSPACE) -> int:
+    """Make sure the split-K scratch of torch's current stream on ``device`` holds at least ``nbytes``
+    (default 8 MiB), so that later calls on that stream, inside a CUDA graph capture included, never
+    have to grow it.  ``ap_matmul_kbit_workspace_bytes(M, N, splits)`` / ``ap_gemm_kbit_workspace_bytes``
+    of the C ABI give the need of a call.  Returns the size now reserved."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(device):
+        ws = _workspace_bytes(device, _current_stream(device), int(nbytes))
+    if ws is None:
+        raise RuntimeError("reserve_workspace cannot allocate while the stream is being captured")
+    return ws.numel()
 
 
 def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bits: int, *,

@@ -45,7 +45,8 @@ class OneShotAllReduce:
     """Sum fp16 CUDA tensors over the ranks of ``group`` (all on one node, one GPU each).
 
     ``max_payload_bytes`` bounds ``tensor.numel() * 2``.  All ranks must construct the object
-    together and then issue the same sequence of calls with the same sizes."""
+    together and then issue the same sequence of calls (call by call the same size on every rank;
+    consecutive calls may differ in size)."""
 
     def __init__(self, max_payload_bytes: int, device: torch.device, group=None):
         self.lib = _lib()
@@ -55,6 +56,8 @@ class OneShotAllReduce:
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         self.device = torch.device(device)
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.max_payload = int(max_payload_bytes)
         self._mine = ctypes.c_void_p()
         self._opened = []
@@ -87,11 +90,17 @@ class OneShotAllReduce:
     def __call__(self, tensor: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         if tensor.dtype != torch.float16 or not tensor.is_cuda or not tensor.is_contiguous():
             raise TypeError("OneShotAllReduce needs a contiguous float16 CUDA tensor")
+        if tensor.device != self.device:
+            raise ValueError(f"tensor is on {tensor.device}, the communication buffers are on {self.device}")
         if out is None:
             out = tensor
-        rc = self.lib.ap_allreduce_oneshot(tensor.data_ptr(), out.data_ptr(), tensor.numel(), self._table, self.rank,
-                                           self.world, self.max_payload, self.status.data_ptr(),
-                                           torch.cuda.current_stream().cuda_stream)
+        elif out.dtype != torch.float16 or not out.is_contiguous() or out.numel() != tensor.numel() \
+                or out.device != self.device:
+            raise ValueError("out must be a contiguous float16 tensor of the same size on the same device")
+        with torch.cuda.device(self.device):
+            rc = self.lib.ap_allreduce_oneshot(tensor.data_ptr(), out.data_ptr(), tensor.numel(), self._table,
+                                               self.rank, self.world, self.max_payload, self.status.data_ptr(),
+                                               torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "ap_allreduce_oneshot")
         return out
 

@@ -18,9 +18,6 @@ Layout (one process per GPU, ``torch.distributed``):
 from __future__ import annotations
 
 import dataclasses
-import json
-import os
-import statistics
 
 import torch
 import torch.distributed as dist
@@ -85,185 +82,21 @@ def shard_forward(x: torch.Tensor, shard: LinearShard, w_bits: int, matmul, grou
     return y
 
 
-# ----------------------------------------------------------------------------------------- benchmark
-def bench_tensor_parallel(args, rank, world, device, gemv_bytes, ClockSampler, measured_peak_gbs, metric, unit,
-                          layer_set, w_bits_all):
-    """Decode-step linear stack of Llama-2-70B, tensor-parallel over ``world`` ranks.
-
-    Per decoder layer: q/k/v (column) -> o (row, all-reduce) -> gate/up (column) -> down (row,
-    all-reduce).  The full-size operands are never materialised: each rank draws its own shard
-    directly (uniform codes are i.i.d. bits, so a shard of random planes is a random shard)."""
-    import any_precision_ext as ext
-
-    M = args.batch
-    layers = args.layers
-    gen = torch.Generator(device=device).manual_seed(4000 + rank)
-    shards = []
-    for _ in range(layers):
-        for name, N, K, style in layer_set:
-            if style == "col":
-                n0, n1 = shard_bounds(N, world, rank, 16)
-                q = packing.random_qweight(8, n1 - n0, K, device=device, generator=gen)
-                luts = {w: packing.random_lut(n1 - n0, w, device=device, generator=gen) for w in w_bits_all}
-                shards.append((name, LinearShard("col", q, luts, (n0, n1), (0, K))))
-            else:
-                k0, k1 = shard_bounds(K, world, rank, 128)
-                q = packing.random_qweight(8, N, k1 - k0, device=device, generator=gen)
-                lgen = torch.Generator(device=device).manual_seed(5000 + len(shards))   # replicated tables
-                luts = {w: packing.random_lut(N, w, device=device, generator=lgen) for w in w_bits_all}
-                shards.append((name, LinearShard("row", q, luts, (0, N), (k0, k1))))
-
-    # Layers that read the same activation are stacked by rows into one operand (q/k/v, gate/up):
-    # one launch instead of three or two.  AP_TP_FUSE=0 keeps one launch per layer.
-    fuse = os.environ.get("AP_TP_FUSE", "1") != "0"
-    if fuse:
-        fused, i = [], 0
-        while i < len(shards):
-            j = i + 1
-            while (shards[i][1].style == "col" and j < len(shards) and shards[j][1].style == "col"
-                   and shards[j][1].in_features == shards[i][1].in_features):
-                j += 1
-            if j - i > 1:
-                q, luts = packing.concat_rows([sh.qweight for _, sh in shards[i:j]], [sh.luts for _, sh in shards[i:j]])
-                n_total = q.shape[1]
-                fused.append(("+".join(n for n, _ in shards[i:j]), LinearShard("col", q, luts, (0, n_total), shards[i][1].k_range)))
-            else:
-                fused.append(shards[i])
-            i = j
-        shards = fused
-
-    hidden = layer_set[0][2]
-    x_full = torch.randn((M, hidden), device=device, generator=torch.Generator(device=device).manual_seed(9)).half()
-    bufs = {}
-    for name, sh in shards:
-        bufs.setdefault((sh.style, sh.out_features), torch.empty((M, sh.out_features), device=device, dtype=torch.float16))
-        bufs.setdefault(("in", sh.in_features), torch.randn((M, sh.in_features), device=device).half())
-
-    # Row-parallel outputs are summed by the one-shot peer-memory kernel unless asked otherwise
-    # (AP_TP_ALLREDUCE=nccl) or its set-up fails on this machine, which the JSON line then says.
-    allreduce, allreduce_kind = None, "nccl"
-    if os.environ.get("AP_TP_ALLREDUCE", "oneshot") == "oneshot":
-        try:
-            from .comm import OneShotAllReduce
-            allreduce = OneShotAllReduce(M * max(sh.out_features for _, sh in shards if sh.style == "row") * 2, device)
-            allreduce_kind = "one-shot over peer memory (ap_allreduce_oneshot)"
-        except Exception as exc:                                   # noqa: BLE001 - reported, not hidden
-            allreduce_kind = f"nccl (one-shot set-up failed: {type(exc).__name__}: {exc})"[:200]
-    kinds = [None] * world
-    dist.all_gather_object(kinds, allreduce is not None)
-    if not all(kinds):                                             # all ranks or none
-        allreduce = None
-        if allreduce_kind.startswith("one-shot"):
-            allreduce_kind = "nccl (one-shot set-up failed on another rank)"
-
-    def one_pass(w):
-        for name, sh in shards:
-            xin = x_full if sh.style == "col" else bufs[("in", sh.in_features)]
-            shard_forward(xin, sh, w, ext.matmul_kbit, out=bufs[(sh.style, sh.out_features)], allreduce=allreduce)
-
-    def one_step():
-        for w in w_bits_all:
-            one_pass(w)
-
-    # whole-job algorithmic bytes: what all ranks together stream (tables of row-parallel layers
-    # are replicated and counted once per rank, because every rank reads them)
-    local_bytes_w = {w: sum(gemv_bytes(M, sh.out_features, sh.in_features, w) for _, sh in shards) for w in w_bits_all}
-    t = torch.tensor([float(local_bytes_w[w]) for w in w_bits_all], device=device, dtype=torch.float64)
-    dist.all_reduce(t)
-    total_bytes_w = {w: float(t[i]) for i, w in enumerate(w_bits_all)}
-    bytes_per_step = sum(total_bytes_w.values())
-
-    stream = torch.cuda.Stream(device)
-    with torch.cuda.stream(stream):
-        one_step()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            one_step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(device.index)
-    sampler.start()
-    for _ in range(args.warmup):
-        graph.replay()
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    clocks = sampler.stop()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms[0]) / args.steps
-    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
-
-    # end to end through the operator API with host activations (copies inside the timed region)
-    x_host = torch.randn((M, hidden)).half().pin_memory()
-    y_host = torch.empty((M, hidden), dtype=torch.float16).pin_memory()
-    x_dev = torch.empty((M, hidden), device=device, dtype=torch.float16)
-
-    def e2e_step():
-        h2d = d2h = 0
-        for w in w_bits_all:
-            for name, sh in shards:
-                if sh.style == "col":
-                    x_dev.copy_(x_host, non_blocking=True)
-                    h2d += x_host.numel() * 2
-                    shard_forward(x_dev, sh, w, ext.matmul_kbit)
-                else:
-                    y = shard_forward(bufs[("in", sh.in_features)], sh, w, ext.matmul_kbit, allreduce=allreduce)
-                    y_host.copy_(y, non_blocking=True)
-                    d2h += y.numel() * 2
-        return h2d, d2h
-
-    e2e_step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(1, min(args.steps, 3))
-    a.record()
-    for _ in range(e2e_steps):
-        h2d, d2h = e2e_step()
-    b.record()
-    torch.cuda.synchronize()
-    ems = torch.tensor([a.elapsed_time(b)], device=device, dtype=torch.float64)
-    dist.all_reduce(ems, op=dist.ReduceOp.MAX)
-    e2e_gbs = bytes_per_step * e2e_steps / (float(ems[0]) * 1e-3) / 1e9
-
-    peak, peak_kind = measured_peak_gbs()
-    line = None
-    if rank == 0:
-        launches = len(shards) * len(w_bits_all)
-        # a decode step of the full 80-layer model streams 80/layers times one pass of this stack
-        tok_s = {str(w): None for w in w_bits_all}
-        line = {
-            "metric": metric, "value": round(value, 1), "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"llama2-70b linear-layer set x{layers} layers, tensor-parallel tp{world} "
-                                   f"(q/k/v/gate/up on N, o/down on K + all-reduce), matmul_kbit M={M}, w_bits 3..8 sweep",
-                       "allreduce": allreduce_kind,
-                       "fused_layers": "q+k+v and gate+up stacked by rows (one launch each)" if fuse else "none",
-                       "batch": M, "parallelism": f"tp{world}", "launches_per_step_per_rank": launches,
-                       "allreduces_per_step": 2 * layers * len(w_bits_all), "bytes_per_step": bytes_per_step,
-                       "l2": "inputs larger than L2"},
-            "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peak, "peak_kind": peak_kind,
-                         "unit": "GB/s per GPU", "frac": round(value / world / peak, 4), "traffic": None},
-            "e2e": {"value": round(e2e_gbs, 1), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches * args.steps,
-            "clocks": clocks,
-        }
-        print(json.dumps(line))
-    # A captured graph holds NCCL work; release it before the communicator goes away, and leave
-    # without the process-group destructor (it can block on a communicator that graphs still use).
-    del graph
-    torch.cuda.synchronize()
-    dist.barrier()
-    import sys
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+def stack_column_shards(shards):
+    """Stack consecutive column-parallel shards that read the same activation (q/k/v, gate/up) into one
+    operand by rows (``packing.concat_rows``): one launch instead of several.  ``shards`` is a list of
+    ``(name, LinearShard)``; row-parallel shards and lone column shards pass through."""
+    fused, i = [], 0
+    while i < len(shards):
+        j = i + 1
+        while (shards[i][1].style == "col" and j < len(shards) and shards[j][1].style == "col"
+               and shards[j][1].in_features == shards[i][1].in_features):
+            j += 1
+        if j - i > 1:
+            q, luts = packing.concat_rows([sh.qweight for _, sh in shards[i:j]], [sh.luts for _, sh in shards[i:j]])
+            fused.append(("+".join(n for n, _ in shards[i:j]),
+                          LinearShard("col", q, luts, (0, q.shape[1]), shards[i][1].k_range)))
+        else:
+            fused.append(shards[i])
+        i = j
+    return fused

@@ -4,6 +4,8 @@
 
 #include <stdio.h>
 
+#include <mutex>
+
 namespace {
 
 thread_local char g_cuda_err[256] = "";
@@ -126,9 +128,12 @@ static __device__ __align__(256) unsigned char ap_builtin_scratch[kBuiltinScratc
 
 namespace {
 
-// Device address of ap_builtin_scratch on the current device (resolved once per device).
+// Device address of ap_builtin_scratch on the current device (resolved once per device; host threads
+// that race for the first call on a device are serialised, and only one of them issues the clear).
 int builtin_scratch(void** ptr, cudaStream_t stream) {
     static void* addr[64] = {};
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -154,7 +159,12 @@ extern "C" size_t ap_builtin_scratch_bytes(void) { return kBuiltinScratchBytes; 
 
 extern "C" int ap_matmul_kbit_splitk_noalloc(const void* x, const void* qweight, int64_t plane_stride, const void* lut,
                                              void* out, int M, int N, int K, int w_bits, int splits, void* stream) {
-    if (splits < 1 || M < 1 || N < 1) return AP_ERR_BAD_SHAPE;
+    if (splits < 1 || M < 1 || N < 1 || K < 32) return AP_ERR_BAD_SHAPE;
+    // The split count the kernel will really use: never more ranges than 1024-weight groups, and none
+    // at all on the shapes that take the plain kernel.  The scratch limit applies to that count.
+    const int groups = (K + 1023) / 1024;
+    if (splits > groups) splits = groups;
+    if (!ap::gemv_fast_path(x, qweight, plane_stride, lut, N, K)) splits = 1;
     if (splits > 1 && ap_matmul_kbit_workspace_bytes(M, N, splits) > kBuiltinScratchBytes) return AP_ERR_SCRATCH_LIMIT;
     void* scratch = nullptr;
     if (splits > 1) {

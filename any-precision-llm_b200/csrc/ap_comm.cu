@@ -5,20 +5,27 @@
 // sizes (M*N*2 bytes = 16..128 KB) a ring or tree collective is all latency, so here every rank
 //   1. stores its partial into slot `rank` of an inbox on EVERY rank (plain 16-byte stores through
 //      NVLink / NVSwitch peer mappings, nothing else),
-//   2. publishes a per-block sequence number on every rank (release, system scope),
+//   2. publishes the call's sequence number, per block, on every rank (release, system scope),
 //   3. waits until the same block of every rank has published that number (acquire, bounded),
 //   4. adds the `world` slots of its own inbox in rank order with fp32 accumulation and writes fp16.
 // The rank order is the same everywhere, so all ranks end with bit-identical results.
 //
 // Memory: one communication buffer per rank, allocated here with cudaMalloc and exchanged between
 // the processes of one node as CUDA IPC handles (ap_comm_* below).  Layout of a buffer:
-//   [0, 4 KB)           seq[kMaxBlocks]            this rank's per-block sequence numbers (private)
+//   [0, 4 KB)           header (private): word 0 = calls completed, word 1 = blocks of the running
+//                       call that are done, word 2 = error word
 //   [4 KB, 20 KB)       flags[kMaxWorld][kMaxBlocks] written by the peers, 32 bytes apart
 //   then                inbox[2][kMaxWorld][cap]    two generations, used in turn
-// The sequence numbers live on the device, so a captured CUDA graph can be replayed: every launch
-// reads its block's number, adds one, and all ranks advance in step because they issue the same
-// sequence of calls.  Two inbox generations are enough: a rank can be at most one call ahead of
-// the slowest rank, because to finish a call it must have seen every rank's flag for that call.
+// The call counter lives on the device, so a captured CUDA graph can be replayed: every block of a
+// launch reads it (after the previous kernel in the stream is over), the call's number is that
+// plus one, and the block that finishes last writes it back.  All ranks advance in step because
+// they issue the same sequence of calls.  The inbox generation is the call number's low bit, the
+// same for every block of a call whatever its size, so consecutive calls always alternate
+// generations even when their element counts (and with them the number of blocks and each
+// block's range) differ.  Two generations are enough: a rank finishes call c only after it has
+// seen a flag of call c from every rank, a rank publishes its first flag of call c only after
+// all of its call c-1 is over (stream order), so when a fast rank stores call c+1 into the
+// generation that call c-1 used, every rank is done reading call c-1.
 //
 // Every wait is bounded.  When one runs out the block records it in `status` (if given) and in the
 // buffer's own error word, skips the reduction and returns; nothing can spin forever.
@@ -74,18 +81,18 @@ __global__ void __launch_bounds__(kThreads)
 allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* __restrict__ out, int n_vec, int rank,
                          int world, size_t cap, int* __restrict__ status) {
     unsigned char* mine = peers.buf[rank];
-    uint32_t* seq_slot = reinterpret_cast<uint32_t*>(mine) + blockIdx.x;
+    uint32_t* header = reinterpret_cast<uint32_t*>(mine);      // [0] calls, [1] blocks done, [2] error
     __shared__ uint32_t s_seq;
     __shared__ int s_ok;
     // Launched as a programmatic dependent of the kernel that produces `src` (the row-parallel
     // matmul_kbit), so that this kernel's launch overlaps that kernel's tail; the next kernel in the
     // stream may start its own prologue now and finds `out` complete when its dependency wait
-    // returns.  Nothing of this kernel's state is read before the wait: the sequence number was
+    // returns.  Nothing of this kernel's state is read before the wait: the call counter was
     // written by the previous call of this kernel, which is only known to be over after it.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
-        s_seq = *seq_slot + 1u;
+        s_seq = __ldcg(header) + 1u;
         s_ok = 1;
     }
     __syncthreads();
@@ -118,12 +125,23 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
         if (!seen) atomicExch(&s_ok, 0);
     }
     __syncthreads();
+    // Every block reads the call counter before it gets here, so the block that counts itself
+    // last may advance it: the next call (after this kernel in stream order) then sees seq.
+    auto finish = [&]() {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            if (atomicAdd(header + 1, 1u) == gridDim.x - 1) {
+                header[1] = 0u;
+                __stcg(header, seq);
+            }
+        }
+    };
     if (!s_ok) {
         if (threadIdx.x == 0) {
             if (status) atomicExch(status, 1);
-            reinterpret_cast<uint32_t*>(mine)[kMaxBlocks] = 1u;      // the buffer's own error word
-            *seq_slot = seq;                                        // stay in step with the other ranks
+            header[2] = 1u;                                         // the buffer's own error word
         }
+        finish();                                                   // stay in step with the other ranks
         return;
     }
     // 4. reduce in rank order
@@ -142,7 +160,7 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
         r.w = f2h(acc[6], acc[7]);
         out[v] = r;
     }
-    if (threadIdx.x == 0) *seq_slot = seq;
+    finish();
 }
 
 thread_local char g_comm_err[256] = "";

@@ -8,28 +8,37 @@
 // leaves the SM.
 //
 // Orientation.  The MMA's M side (128 TMEM lanes) is a block of 128 weight rows, its N side is a
-// block of BM tokens: D[n][m] += A[n][k] * B[m][k], both operands K-major in shared memory with
-// the 128-byte swizzle.  The reduction order over k is free, so a k-tile is taken in the packed
-// order of the operand: the 64 weights of two consecutive plane words of a row, i.e. eight runs
-// of eight consecutive weights (ap_bitplane.cuh).  A 16-byte swizzle chunk is exactly one run,
-// for the weights (produced by the bit transpose + table lookups) and for the activations
-// (gathered with 16-byte cp.async from the matching eight-element run of x).
+// block of BM tokens (64, 128 or 256): D[n][m] += A[n][k] * B[m][k].  The reduction order over k is
+// free, so k-tiles follow the packed format: eight consecutive plane words of a row hold 256
+// weights whose byte group j (j = 0..3) is a run of 64 CONSECUTIVE weights, so k-tile (words
+// 8u..8u+7, byte group j) needs a plain [BM tokens][64 halfs] box of x: one tiled TMA copy,
+// swizzled by the TMA unit.  Four such k-tiles make a super-tile, the unit a producer thread
+// dequantises from one bit transpose of its words.
 //
-// Roles in a CTA:
-//   warps 0-7  producers: two threads per weight row of the block; per k-tile each dequantises 32
-//              weights (one plane word) into the A stage.  After the main loop the same warps drain
-//              TMEM (tcgen05.ld), convert to fp16 and store the transposed result.
-//   warp 8     allocates TMEM; one lane issues the MMAs of each stage and commits them to the
-//              stage's "empty" mbarrier; a final commit signals the epilogue.
-//   warp 9     (K a multiple of 256) one lane brings each stage's activations in with ONE tiled TMA
-//              copy.  For that the k-tiles are cut differently: eight consecutive plane words of a
-//              row hold 256 weights whose byte group j (j = 0..3) is a run of 64 CONSECUTIVE
-//              weights, so k-tile (words 8u..8u+7, byte group j) is a plain [BM tokens][64 halfs] box
-//              of x, 128-byte swizzled by the TMA unit.  A producer thread then owns four of the
-//              eight words (one 16-byte plane load per plane), transposes them once and feeds four
-//              k-tiles from the result.  For other K the producers take k-tiles of two words and
-//              gather the eight scattered runs of x with 16-byte cp.async, signalling a stage one
-//              k-tile late, when their copies have landed.
+// The template parameter TM selects how the operands travel (the default, for K % 256 == 0, is 3):
+//   TM = 3  planes by tiled TMA ([w][128 rows][8 or 16 words] boxes into a double buffer), sixteen
+//           producer warps (four threads per weight row); the dequantised weights go straight into
+//           TENSOR MEMORY (tcgen05.st into a ring of 128-column super-stages beside the accumulator,
+//           the producer's row being its TMEM lane) and the MMA takes A from tensor memory; the
+//           shared memory goes to the activation ring.  w = 3 looks its table up from registers.
+//   TM = 2  the same loaders, but A is stored as 16-byte swizzled chunks in shared-memory stages
+//           (fence.proxy.async) and read from there by the MMA.
+//   TM = 1  as TM = 2 with the planes read from global memory by the producers (one 16-byte load
+//           per plane, thread and eight words): where two plane buffers would not leave three stages.
+//   TM = 0  K % 256 != 0: k-tiles of two words; eight producer warps gather the eight scattered
+//           runs of x with 16-byte cp.async, signalling a stage when their copies have landed.
+//
+// Roles in a CTA (TM >= 2; TM <= 1 has eight producer warps):
+//   warps 0-15 producers: dequantise, then, after the main loop, drain TMEM (tcgen05.ld), convert
+//              to fp16 and store the transposed tile (or park fp32 partials for split-K).
+//   warp 16    allocates TMEM; one lane issues four tcgen05.mma.cta_group::1.kind::f16 per k-tile
+//              and one tcgen05.commit per super-tile.  For token blocks up to 128 a further warp is a
+//              second issuer: each takes every other super-tile into an accumulator of its own and
+//              the read-out adds the two (rings have an even number of hand-over units, so that a
+//              barrier is always waited on by the same issuer).
+//   warp 17    one lane issues the TMA copies (planes two groups ahead, activations as stages free).
+// The kernel is a programmatic-dependent-launch secondary: TMEM allocation, barriers, tables and
+// the first plane boxes come before the dependency wait, activations and the output after it.
 // Every wait is bounded: on expiry the kernel raises a status flag, skips the remaining work,
 // still frees its tensor memory and returns.
 #include <cstdlib>

@@ -1,30 +1,29 @@
-// matmul_kbit (decode GEMV, 1 <= M <= 8) for sm_100a:
+// matmul_kbit (decode GEMV) for sm_100a:
 //     y[m][n] = sum_k x[m][k] * lut[n][code_w(n,k)]
 // with fp32 accumulation.  Replaces the reference's matmul_kbit host function and its
 // matmul_kbit_32<maxm,bits,use_ksplit> kernels (any_precision/modules/kernels/main.cu:93-143,
 // matmul.cuh:16-167), which accumulate in fp16 with one multiply-add per weight per batch row.
 //
-// What bounds this kernel on a B200 is instruction issue (4 warp-instructions per clock per
-// SM), not shared-memory bandwidth: at HBM speed an SM has a budget of about 2 (w = 3) to 5.5
-// (w = 8) instructions per weight.  The kernel is therefore built to spend as few instructions
-// per weight as possible:
-//   * a CTA owns 16 output rows and its warps split K; a lane streams, for its two rows and
-//     each of the top w planes, 16- or 8-byte pieces with cp.async into a private
-//     shared-memory ring (two stages), so HBM latency is hidden without holding registers;
-//   * plane words are transposed into byte-packed codes in registers (ap_bitplane.cuh); for
-//     w <= 7 the code is produced pre-multiplied by the entry size, so one PRMT merges it
-//     with the table base into a shared-memory address;
-//   * for w <= 4 the transpose works on nibbles and a byte indexes a table of weight PAIRS
-//     (fp16x2), halving the lookups; bank conflicts are left alone, the LSU absorbs them;
-//   * the dot products run on the tensor pipe (mma.sync m16n8k16, fp32 accumulators): the 16
-//     rows are the M side and the batch (up to 8) the N side, so batch 1..8 cost the same and
-//     no multiply-add is ever issued per weight;
-//   * activations are read straight into B fragments (L1-resident after first touch).
-// The kernel is a programmatic-dependent-launch secondary: it streams weights and builds its
-// tables before waiting for the previous kernel in the stream, and lets the next one start
-// as soon as its own plane reads are in flight.
-// Everything else (K not a multiple of 128, N not a multiple of 16, unaligned pointers) takes
-// the plain kernel at the bottom, one warp per row.
+// This file holds
+//   * the pieces every decode kernel shares: the lookup helpers (PRMT-built table addresses), the
+//     mma.sync wrapper and process_word, which turns one plane word of two rows into eight MMAs;
+//   * launch_gemv, which picks a kernel for a call;
+//   * two fallback kernels: gemv_kbit_mma_kernel (per-lane cp.async ring; taken when the planes
+//     cannot be described to the TMA unit, or with AP_GEMV_LOADER=cpasync) and
+//     gemv_kbit_plain_kernel (one warp per row, fp32 multiply-adds; for K % 128 != 0, N % 16 != 0
+//     or unaligned pointers).
+// The kernel that runs by default, gemv_kbit_tma_kernel, is in ap_gemv_tma.cuh (included below).
+//
+// Common design.  A thread block owns 16 output rows and its eight warps split K.  Plane words
+// are transposed into byte-packed codes in registers (ap_bitplane.cuh); a code byte and the
+// lane's byte offset form a shared-memory address with one PRMT; for w <= 4 a byte holds the
+// codes of TWO weights and indexes a table of fp16 pairs, halving the lookups.  The dot products
+// run on the tensor pipe (mma.sync m16n8k16, fp32 accumulators) with the 16 rows on the M side
+// and the batch (up to 8) on the N side, so batch 1..8 cost the same and no multiply-add is
+// issued per weight.  What bounds the arithmetic on a B200 is instruction issue and the integer
+// ALU pipe (bit transposes and address permutes), not shared-memory bandwidth and not HBM.
+// The kernels are programmatic-dependent-launch secondaries: they request weights and build
+// their tables before waiting for the previous kernel in the stream and read activations after.
 #include "ap_bitplane.cuh"
 #include "ap_kernels.h"
 
@@ -90,18 +89,32 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 constexpr int kGemvMaxWarps = 8;
 
 #ifdef AP_GEMV_PROFILE
-// Lab builds only: per-CTA timestamps of the kernel's phases (never compiled into the library).
-__device__ unsigned long long ap_gemv_prof[8 * 4096];
-__device__ __forceinline__ void prof_mark(int slot) {
-    if (threadIdx.x == 0 && blockIdx.x < 4096) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        ap_gemv_prof[blockIdx.x * 8 + slot] = t;
+// Lab builds only: per-block stamps of the kernel's phases (never compiled into the library).
+// A launch is told apart by its output pointer: launch l writes out_base + l * out_stride bytes.
+constexpr int kProfLaunches = 16, kProfBlocks = 1024, kProfSlots = 16;
+__device__ unsigned long long ap_gemv_prof[kProfLaunches * kProfBlocks * kProfSlots];
+__device__ const char* ap_prof_out_base;
+__device__ long long ap_prof_out_stride;
+__device__ __forceinline__ unsigned long long* prof_init(const void* out) {
+    if (threadIdx.x == 0 && blockIdx.x < kProfBlocks && blockIdx.y == 0 && ap_prof_out_stride > 0) {
+        const long long l = (static_cast<const char*>(out) - ap_prof_out_base) / ap_prof_out_stride;
+        if (l >= 0 && l < kProfLaunches) return ap_gemv_prof + (l * kProfBlocks + blockIdx.x) * kProfSlots;
     }
+    return nullptr;
 }
-#define AP_PROF(slot) prof_mark(slot)
+__device__ __forceinline__ void prof_mark(unsigned long long* p, int slot) {
+    if (p) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); p[slot] = t; }
+}
+__device__ __forceinline__ void prof_clk(unsigned long long* p, int slot) {
+    if (p) p[slot] = (unsigned long long)clock64();
+}
+#define AP_PROF_INIT unsigned long long* ap_prof_p = prof_init(out)
+#define AP_PROF(slot) prof_mark(ap_prof_p, slot)
+#define AP_CLK(slot) prof_clk(ap_prof_p, slot)
 #else
+#define AP_PROF_INIT
 #define AP_PROF(slot)
+#define AP_CLK(slot)
 #endif
 
 template <int W>
@@ -137,7 +150,9 @@ template <int W, int MODE = 0>
 __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint32_t (&wb)[W], const uint4 (&xv)[4],
                                              float (&acc)[2][4], const uint32_t (&lut_lo)[2][2],
                                              const uint32_t (&lut_hi)[2][2], uint32_t tab_a, uint32_t tab_b,
-                                             uint32_t tab_const = 0u) {
+                                             uint32_t tab_const = 0u, bool valid = true) {
+    // `valid` false (a word past the end of a short last group): the weights are taken as zero
+    // without looking anything up, so that no table entry, finite or not, meets the (zeroed) activations.
     using Cfg = GemvCfg<W>;
     if constexpr (MODE == 2 || Cfg::kRegLut) {
         uint32_t na[4], nb[4];
@@ -148,10 +163,15 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             if constexpr (MODE == 2) {
+                if (valid) {
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    wq[0][c][j] = lds_u32(tab_const + entry_offset_direct(na[c], 3 - j, tab_a));
-                    wq[1][c][j] = lds_u32(tab_const + entry_offset_direct(nb[c], 3 - j, tab_b));
+                    for (int j = 0; j < 4; j++) {
+                        wq[0][c][j] = lds_u32(tab_const + entry_offset_direct(na[c], 3 - j, tab_a));
+                        wq[1][c][j] = lds_u32(tab_const + entry_offset_direct(nb[c], 3 - j, tab_b));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) wq[0][c][j] = wq[1][c][j] = 0u;
                 }
             } else {
 #pragma unroll
@@ -165,6 +185,10 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
                     wq[0][c][2 - 2 * hs] = __byte_perm(alo, ahi, 0x7362);
                     wq[1][c][3 - 2 * hs] = __byte_perm(blo, bhi, 0x5140);
                     wq[1][c][2 - 2 * hs] = __byte_perm(blo, bhi, 0x7362);
+                }
+                if (!valid) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) wq[0][c][j] = wq[1][c][j] = 0u;
                 }
             }
         }
@@ -189,15 +213,17 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
         for (int j = 0; j < 4; j++) {
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                uint32_t va[4], vb[4];
+                uint32_t va[4] = {0u, 0u, 0u, 0u}, vb[4] = {0u, 0u, 0u, 0u};
+                if (valid) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    if constexpr (MODE == 1) {
-                        va[e] = lds_u16(tab_const + entry_offset_direct(ca[4 * h + e], 3 - j, tab_a));
-                        vb[e] = lds_u16(tab_const + entry_offset_direct(cb[4 * h + e], 3 - j, tab_b));
-                    } else {
-                        va[e] = lds_u16(entry_addr<128>(ca[4 * h + e], 3 - j, tab_a));
-                        vb[e] = lds_u16(entry_addr<128>(cb[4 * h + e], 3 - j, tab_b));
+                    for (int e = 0; e < 4; e++) {
+                        if constexpr (MODE == 1) {
+                            va[e] = lds_u16(tab_const + entry_offset_direct(ca[4 * h + e], 3 - j, tab_a));
+                            vb[e] = lds_u16(tab_const + entry_offset_direct(cb[4 * h + e], 3 - j, tab_b));
+                        } else {
+                            va[e] = lds_u16(entry_addr<128>(ca[4 * h + e], 3 - j, tab_a));
+                            vb[e] = lds_u16(entry_addr<128>(cb[4 * h + e], 3 - j, tab_b));
+                        }
                     }
                 }
                 const uint32_t a0 = __byte_perm(va[0], va[1], 0x5410), a2 = __byte_perm(va[2], va[3], 0x5410);
@@ -281,6 +307,7 @@ gemv_kbit_mma_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ 
                                  xrow + kbase + 8 * wd + kstride * j);
         }
     };
+    AP_PROF_INIT;
     AP_PROF(0);
     // Tables first: their source rows are requested before the (much larger) plane stream, so
     // that they do not queue behind it in the memory system.
@@ -411,14 +438,14 @@ gemv_kbit_mma_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ 
                                  : "=r"(xv[j].x), "=r"(xv[j].y), "=r"(xv[j].z), "=r"(xv[j].w)
                                  : "r"(xs + (wd * 4 + j) * x_item_bytes));
                 if (!valid) {
-                    // Lanes past the end of the row hold stale ring contents: give them code 0 and
-                    // zero activations (tables are assumed finite).
+                    // Lanes past the end of the row hold stale ring contents: zero activations
+                    // against weights that process_word takes as zero without a lookup.
 #pragma unroll
                     for (int p = 0; p < W; p++) wa[p] = wb[p] = 0u;
 #pragma unroll
                     for (int j = 0; j < 4; j++) xv[j] = make_uint4(0u, 0u, 0u, 0u);
                 }
-                process_word<W>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b);
+                process_word<W>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, 0u, valid);
             }
         }
         // the stage just consumed is free: refill it with the step after next

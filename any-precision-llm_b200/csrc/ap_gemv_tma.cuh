@@ -14,7 +14,8 @@
 // so that the eight rows a half-warp reads do not all sit in the same banks.  The chunk's
 // activations follow in natural order (plain bulk copies, one per batch row).  Each buffer has a
 // `full` mbarrier that counts the bytes in.  A chunk is four steps of 8 words; step s goes to warp
-// s % 8; the warp that finishes a chunk's fourth step re-arms the buffer with a later chunk.
+// s % 8; the warp that took a chunk's first step waits for the other three (an `empty` mbarrier per
+// buffer, one arrival per warp) and re-arms the buffer with a later chunk.
 // Waits are bounded: on expiry the warp records it in ap_gemv_wait_expired and stops working.
 #pragma once
 
@@ -27,10 +28,14 @@
 namespace ap {
 
 constexpr int kTmaChunkWords = 32;
+constexpr int kTmaRingCap = 4;                             // chunk buffers per block at most (deeper rings measured no faster)
 constexpr int kTmaXPitch = 1024 * 2 + 16;                  // bytes per batch row of a chunk's activations
 constexpr uint32_t kTmaSpinLimit = 1u << 17;
 
 __device__ int ap_gemv_wait_expired = 0;
+
+struct TrueType { static constexpr bool value = true; };
+struct FalseType { static constexpr bool value = false; };
 
 // OCC: thread blocks per SM the kernel variant is built for (2 or 3).  Three blocks need a
 // register cap of 80, which costs instruction-level parallelism, and a smaller shared-memory
@@ -62,7 +67,7 @@ struct GemvTmaCfg {
     __host__ __device__ static constexpr int buffers(int mpad) {
         const int fixed = 1024 + kTableBytes + GemvCfg<W>::kRedBytes + 256;
         const int n = ((OCC == 3 ? 74 : 110) * 1024 - fixed) / buffer_bytes(mpad);
-        return n > 4 ? 4 : (n < 2 ? 2 : n);
+        return n > kTmaRingCap ? kTmaRingCap : (n < 2 ? 2 : n);
     }
     __host__ __device__ static constexpr int total(int mpad) {
         return 1024 + buffers(mpad) * buffer_bytes(mpad) + kTableBytes + GemvCfg<W>::kRedBytes + 256;
@@ -115,7 +120,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     unsigned char* bufs = smem;                                           // 1024-byte aligned boxes
     float* red = reinterpret_cast<float*>(smem + nbuf * buf_bytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(red) + Cfg::kRedBytes);   // full[nbuf][2]
-    int* done_count = reinterpret_cast<int*>(bars + 8);                    // per buffer: steps finished
+    // then empty[nbuf]: one arrival per warp that has finished its step of the buffer's chunk
 
     // More than eight batch rows (no split-K then): blockIdx.z takes rows [8 z, 8 z + 8) of x and out, so
     // that the passes over the planes run side by side in one launch and the later ones read them from L2.
@@ -167,12 +172,13 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
         __syncwarp();
     };
 
+    AP_PROF_INIT;
     AP_PROF(0);
     if (tid == 0) {
         for (int b = 0; b < nbuf; b++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_sh + 16u * b), "r"(2u) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_sh + 16u * b + 8u), "r"(2u) : "memory");
-            done_count[b] = 0;
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_sh + 16u * kTmaRingCap + 8u * b), "r"(4u) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&qmap)) : "memory");
@@ -284,6 +290,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
 
     // Activations (and the output) may come from the previous kernel in the stream.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    AP_PROF(7);
     if (warp == 0) {
         for (int i = 0; i < first; i++) request_x(i);
     }
@@ -319,37 +326,55 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
             // run j of word wd inside the chunk's activations: element 8*(wic + wd) + 8*cw_words*j
             const uint32_t xw = buf + x_lane + (uint32_t)wic * 16u;
             const uint32_t xj = (uint32_t)cw_words * 16u;
+            // A step is either whole (all of its eight words lie inside the row: every step of every
+            // full 1024-weight group, and most steps of a short last group) or cut (K / 32 % 8 == 4: the
+            // lanes t >= 2 of the last step have no words).  The whole case is compiled with the mask
+            // as a constant, so that the common path carries no selects or branches for it.
+            auto two_words = [&](auto whole) {
+                constexpr bool kWhole = decltype(whole)::value;
+                const bool valid_w = kWhole || valid;
 #pragma unroll
-            for (int wd = 0; wd < 2; wd++) {
-                uint32_t wa[W], wb[W];
+                for (int wd = 0; wd < 2; wd++) {
+                    uint32_t wa[W], wb[W];
 #pragma unroll
-                for (int p = 0; p < W; p++) { wa[p] = pa[p][wd]; wb[p] = pb[p][wd]; }
-                uint4 xv[4];
+                    for (int p = 0; p < W; p++) { wa[p] = pa[p][wd]; wb[p] = pb[p][wd]; }
+                    // Only the lanes of batch columns that exist (g < mpad) load activations; the MMA's other
+                    // columns are never stored.
+                    uint4 xv[4] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u),
+                                   make_uint4(0u, 0u, 0u, 0u)};
+                    if (g < mpad) {
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(xv[j].x), "=r"(xv[j].y), "=r"(xv[j].z), "=r"(xv[j].w)
-                                 : "r"(xw + wd * 16 + j * xj));
-                if (!valid) {
-                    // Words past the end of the row: the box holds zeros there, the activation
-                    // area holds leftovers.  Code 0 times zero activations contributes nothing.
+                        for (int j = 0; j < 4; j++)
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(xv[j].x), "=r"(xv[j].y), "=r"(xv[j].z), "=r"(xv[j].w)
+                                         : "r"(xw + wd * 16 + j * xj));
+                    }
+                    if (!valid_w) {
+                        // Words past the end of the row: the box holds zeros there, the activation
+                        // area holds leftovers.  Zero activations against weights that process_word
+                        // takes as zero without a lookup.
 #pragma unroll
-                    for (int p = 0; p < W; p++) wa[p] = wb[p] = 0u;
+                        for (int p = 0; p < W; p++) wa[p] = wb[p] = 0u;
 #pragma unroll
-                    for (int j = 0; j < 4; j++) xv[j] = make_uint4(0u, 0u, 0u, 0u);
+                        for (int j = 0; j < 4; j++) xv[j] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    process_word<W, T::kMode>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, table_const, valid_w);
                 }
-                process_word<W, T::kMode>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, table_const);
-            }
+            };
+            if (8 * sl + 8 <= cw_words) two_words(TrueType{});
+            else two_words(FalseType{});
         }
-        // This warp is done with the buffer; the fourth one to say so re-arms it.
+        // This warp is done with the buffer (its plane words and activations are in registers or
+        // consumed): it says so on the buffer's `empty` barrier and moves on.  The warp that took the
+        // chunk's first step waits for all four and re-arms the buffer with a later chunk; the other
+        // three never wait for one another.
         __syncwarp();
-        int last = 0;
-        if (lane == 0) last = (atomicAdd(&done_count[b], 1) == 3);
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last && ok) {
-            if (lane == 0) done_count[b] = 0;
-            const int inext = i + nbuf;
-            if (inext < nchunks) {
+        const uint32_t empty = bar_sh + 16u * kTmaRingCap + 8u * (uint32_t)b;
+        if (lane == 0) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(empty) : "memory");
+        const int inext = i + nbuf;
+        if (sl == 0 && ok && inext < nchunks) {
+            ok = mbar_wait_bounded(empty, (uint32_t)(i / nbuf) & 1u);
+            if (ok) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 request_planes(inext);
                 request_x(inext);

@@ -18,8 +18,10 @@ quantity through the public operator API (any_precision_ext.matmul_kbit) with ac
 coming from pinned host memory and results copied back, copies inside the timed region.
 
 At N > 1 the workload is the Llama-2-70B linear-layer set, tensor-parallel over the ranks
-(q/k/v/gate/up split on N, o/down split on K with an NCCL all-reduce of the row-parallel
-outputs); value is again total algorithmic bytes over the max-over-ranks time.
+(q/k/v/gate/up split on N, o/down split on K with an all-reduce of the row-parallel outputs);
+value is again total algorithmic bytes over the max-over-ranks time.  The same workload on one
+GPU (`tp1_llama2_70b` in the N = 1 line) anchors the 1/2/4/8 curve, and `curve` holds w_bits
+3, 4, 8 at batch 1 and 8 with the decode rate the linear stack alone would allow.
 
 `--impl reference` times the reference semantics on the host cores instead: the reference's own
 dequantisation kernel source compiled for the CPU (oracle/_ref; else the oracle port) followed by
@@ -216,9 +218,16 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
 
     if world > 1:
-        from anyprec_b200 import tensor_parallel as tp
-        return tp.bench_tensor_parallel(args, rank, world, device, gemv_bytes, ClockSampler, measured_peak_gbs,
-                                        METRIC, UNIT, LLAMA2_70B_SET, W_BITS)
+        line = tensor_parallel_figures(args, rank, world, device, args.layers, full=True)
+        if rank == 0:
+            print(json.dumps(line))
+        # A captured graph holds collective work; leave without the process-group destructor (it can block
+        # on a communicator that graphs still use).  Only the benchmark process ends this way.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
     M = args.batch
     weights = build_weight_set(torch, packing, LLAMA2_7B_SET, args.layers, device, seed=1000)
@@ -385,6 +394,8 @@ def run_ours(args):
     del egraph
 
     prefill = prefill_figures(torch, ext, packing, device)
+    # The tensor-parallel workload (Llama-2-70B layer set) on this one GPU: the anchor of the 1/2/4/8 curve.
+    tp1 = tensor_parallel_figures(args, 0, 1, device, args.layers, full=False)
     cpu = cpu_baseline_sample(kind_pref="port", seconds_hint=15)
 
     line = {
@@ -397,6 +408,7 @@ def run_ours(args):
         "fused_qkv_gateup": {"value": round(fused_value, 1), "unit": UNIT, "launches_per_step": 4 * args.layers * len(W_BITS),
                              "note": "same weights, q+k+v and gate+up stacked by rows (packing.concat_rows)"},
         "prefill": prefill,
+        "tp1_llama2_70b": tp1,
         "per_w_bits_gbs": per_w,
         "per_w_bits_frac_of_measured_peak": {k: round(v / peak, 3) for k, v in per_w.items()},
         "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
@@ -416,6 +428,245 @@ def run_ours(args):
     }
     print(json.dumps(line))
     return line
+
+
+
+# ----------------------------------------------------------------------------- tensor-parallel workload
+def tensor_parallel_figures(args, rank, world, device, layers, full):
+    """Decode-step linear stack of Llama-2-70B over `world` ranks (world = 1: the whole layers on one GPU).
+
+    Per decoder layer: q+k+v (column-parallel, stacked by rows into one launch) -> o (row-parallel,
+    all-reduce) -> gate+up (column, stacked) -> down (row, all-reduce).  The full-size operands are never
+    materialised: each rank draws its own shard directly (uniform codes are i.i.d. bits, so a shard of
+    random planes is a random shard).  Before anything is timed one row-parallel layer's all-reduced output
+    is checked against a rank-order fp32 sum of the gathered partial results (`tp_check`).
+
+    Returns the JSON line (world > 1, rank 0; None on other ranks) or, for world = 1, the secondary object
+    that the one-GPU line carries."""
+    import torch
+    import torch.distributed as dist
+
+    import any_precision_ext as ext
+    from anyprec_b200 import packing
+    from anyprec_b200.tensor_parallel import LinearShard, shard_bounds, shard_forward, stack_column_shards
+
+    M = args.batch
+    gen = torch.Generator(device=device).manual_seed(4000 + rank)
+    shards = []
+    for _ in range(layers):
+        for name, N, K, style in LLAMA2_70B_SET:
+            if style == "col":
+                n0, n1 = shard_bounds(N, world, rank, 16)
+                q = packing.random_qweight(8, n1 - n0, K, device=device, generator=gen)
+                luts = {w: packing.random_lut(n1 - n0, w, device=device, generator=gen) for w in W_BITS}
+                shards.append((name, LinearShard("col", q, luts, (n0, n1), (0, K))))
+            else:
+                k0, k1 = shard_bounds(K, world, rank, 128)
+                q = packing.random_qweight(8, N, k1 - k0, device=device, generator=gen)
+                lgen = torch.Generator(device=device).manual_seed(5000 + len(shards))   # replicated tables
+                luts = {w: packing.random_lut(N, w, device=device, generator=lgen) for w in W_BITS}
+                shards.append((name, LinearShard("row", q, luts, (0, N), (k0, k1))))
+    fuse = os.environ.get("AP_TP_FUSE", "1") != "0"
+    if fuse:
+        shards = stack_column_shards(shards)
+
+    hidden = LLAMA2_70B_SET[0][2]
+    max_m = 8
+    x_full = torch.randn((max_m, hidden), device=device, generator=torch.Generator(device=device).manual_seed(9)).half()
+    bufs = {}
+    for name, sh in shards:
+        bufs.setdefault((sh.style, sh.out_features), torch.empty((max_m, sh.out_features), device=device, dtype=torch.float16))
+        bufs.setdefault(("in", sh.in_features), torch.randn((max_m, sh.in_features), device=device).half())
+
+    # Row-parallel outputs are summed by the one-shot peer-memory kernel unless asked otherwise
+    # (AP_TP_ALLREDUCE=nccl) or its set-up fails on this machine, which the JSON line then says.
+    allreduce, allreduce_kind = None, "none (one rank)"
+    if world > 1:
+        allreduce_kind = "nccl"
+        if os.environ.get("AP_TP_ALLREDUCE", "oneshot") == "oneshot":
+            try:
+                from anyprec_b200.comm import OneShotAllReduce
+                allreduce = OneShotAllReduce(max_m * max(sh.out_features for _, sh in shards if sh.style == "row") * 2, device)
+                allreduce_kind = "one-shot over peer memory (ap_allreduce_oneshot)"
+            except Exception as exc:                                   # noqa: BLE001 - reported, not hidden
+                allreduce_kind = f"nccl (one-shot set-up failed: {type(exc).__name__}: {exc})"[:200]
+        kinds = [None] * world
+        dist.all_gather_object(kinds, allreduce is not None)
+        if not all(kinds):                                             # all ranks or none
+            allreduce = None
+            if allreduce_kind.startswith("one-shot"):
+                allreduce_kind = "nccl (one-shot set-up failed on another rank)"
+
+    # tp_check: one row-parallel layer, every precision of the curve, batch 1 and 8
+    tp_check = "not applicable (one rank)"
+    if world > 1:
+        name, sh = next((n, s) for n, s in shards if s.style == "row")
+        good = True
+        for m in (1, 8):
+            for w in (3, 4, 8):
+                xin = bufs[("in", sh.in_features)][:m]
+                part = ext.matmul_kbit(xin, sh.qweight, sh.luts[w], w)
+                gathered = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(gathered, part)
+                want = torch.zeros_like(part, dtype=torch.float32)
+                for r in range(world):
+                    want += gathered[r].float()                       # rank order, fp32: what the kernel does
+                got = shard_forward(xin, sh, w, ext.matmul_kbit, allreduce=allreduce)
+                if allreduce is not None:
+                    good = good and torch.equal(got, want.to(torch.float16))
+                else:
+                    good = good and torch.allclose(got.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+        flag = torch.tensor([1.0 if good else 0.0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        tp_check = "ok" if float(flag[0]) == 1.0 else "FAILED"
+        if tp_check != "ok":
+            raise SystemExit(f"tp_check failed on {name}: the all-reduced row-parallel output differs from the sum of the partials")
+
+    def one_pass(w, m, do_gemv=True, do_reduce=True):
+        for name, sh in shards:
+            xin = (x_full if sh.style == "col" else bufs[("in", sh.in_features)])[:m]
+            out = bufs[(sh.style, sh.out_features)][:m]
+            if do_gemv:
+                ext.matmul_kbit(xin, sh.qweight, sh.luts[w], w, out=out)
+            if do_reduce and sh.style == "row" and world > 1:
+                if allreduce is not None:
+                    allreduce(out)
+                else:
+                    dist.all_reduce(out, op=dist.ReduceOp.SUM)
+
+    def local_bytes(w, m):
+        return sum(gemv_bytes(m, sh.out_features, sh.in_features, w) for _, sh in shards)
+
+    def total_bytes(w, m):
+        # whole-job algorithmic bytes: what all ranks together stream (tables of row-parallel layers are
+        # replicated and counted once per rank, because every rank reads them)
+        t = torch.tensor([float(local_bytes(w, m))], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t)
+        return float(t[0])
+
+    stream = torch.cuda.Stream(device)
+    ext.reserve_workspace(device)
+
+    def timed(fn, steps, warmup):
+        """Capture fn into a graph on `stream`, replay it warmup + steps times; ms per replay, max over ranks."""
+        with torch.cuda.stream(stream):
+            ext.reserve_workspace(device)
+            fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+        torch.cuda.synchronize()
+        for _ in range(warmup):
+            g.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        del g
+        return float(ms[0])
+
+    peak, peak_kind = measured_peak_gbs()
+    sampler = ClockSampler(device.index if device.index is not None else 0)
+    sampler.start()
+    time.sleep(0.3)                                                    # nvidia-smi needs a moment to deliver samples
+    ms_per_step = timed(lambda: [one_pass(w, M) for w in W_BITS], args.steps, args.warmup)
+    clocks = sampler.stop()
+    bytes_per_step = sum(total_bytes(w, M) for w in W_BITS)
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # The curve BASELINE.json asks for: w_bits 3, 4, 8 at batch 1 and 8; per-GPU roofline fraction and the
+    # decode rate the linear stack alone would allow for the 80-layer model (attention, norms and sampling
+    # not included).
+    curve = {}
+    short = max(3, args.steps // 2)
+    for m in (1, 8):
+        for w in (3, 4, 8):
+            ms = timed(lambda: one_pass(w, m), short, 3)
+            gbs = total_bytes(w, m) / (ms * 1e-3) / 1e9
+            curve[f"batch{m}_w{w}"] = {
+                "ms_per_pass": round(ms, 4), "gbs": round(gbs, 1), "per_gpu_frac_of_peak": round(gbs / world / peak, 4),
+                "us_per_decoder_layer": round(ms * 1e3 / layers, 2),
+                "tok_s_linear_stack_80_layers": round(m / (ms * 1e-3 / layers * 80), 1)}
+    breakdown = None
+    if world > 1:
+        gemv_ms = timed(lambda: [one_pass(w, M, do_reduce=False) for w in W_BITS], short, 3)
+        red_ms = timed(lambda: [one_pass(w, M, do_gemv=False) for w in W_BITS], short, 3)
+        breakdown = {"gemv_only_ms_per_step": round(gemv_ms, 4), "allreduce_only_ms_per_step": round(red_ms, 4),
+                     "both_ms_per_step": round(ms_per_step, 4),
+                     "note": "the same step captured without the all-reduces and without the GEMVs"}
+
+    launches = len(shards) * len(W_BITS)
+    config = {"workload": f"llama2-70b linear-layer set x{layers} layers, tensor-parallel tp{world} "
+                          f"(q/k/v/gate/up on N, o/down on K + all-reduce), matmul_kbit M={M}, w_bits 3..8 sweep",
+              "allreduce": allreduce_kind, "tp_check": tp_check,
+              "fused_layers": "q+k+v and gate+up stacked by rows (one launch each)" if fuse else "none",
+              "batch": M, "parallelism": f"tp{world}", "launches_per_step_per_rank": launches,
+              "allreduces_per_step": (2 * layers * len(W_BITS)) if world > 1 else 0, "bytes_per_step": bytes_per_step,
+              "l2": "inputs larger than L2"}
+    if not full:
+        return {"value": round(value, 1), "unit": UNIT, "ms_per_step": round(ms_per_step, 4),
+                "frac_of_peak": round(value / peak, 4), "config": config, "curve": curve,
+                "note": "the N > 1 workload on one GPU (no all-reduce): the TP = 1 point of the scaling curve"}
+
+    # end to end through the operator API with host activations (copies inside the timed region)
+    x_host = torch.randn((M, hidden)).half().pin_memory()
+    y_host = torch.empty((M, hidden), dtype=torch.float16).pin_memory()
+    x_dev = torch.empty((M, hidden), device=device, dtype=torch.float16)
+
+    def e2e_step():
+        h2d = d2h = 0
+        for w in W_BITS:
+            for name, sh in shards:
+                if sh.style == "col":
+                    x_dev.copy_(x_host, non_blocking=True)
+                    h2d += x_host.numel() * 2
+                    shard_forward(x_dev, sh, w, ext.matmul_kbit)
+                else:
+                    y = shard_forward(bufs[("in", sh.in_features)][:M], sh, w, ext.matmul_kbit, allreduce=allreduce)
+                    y_host.copy_(y, non_blocking=True)
+                    d2h += y.numel() * 2
+        torch.cuda.current_stream().synchronize()
+        return h2d, d2h
+
+    e2e_step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(1, min(args.steps, 3))
+    a.record()
+    for _ in range(e2e_steps):
+        h2d, d2h = e2e_step()
+    b.record()
+    torch.cuda.synchronize()
+    ems = torch.tensor([a.elapsed_time(b)], device=device, dtype=torch.float64)
+    dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+    e2e_gbs = bytes_per_step * e2e_steps / (float(ems[0]) * 1e-3) / 1e9
+    if rank != 0:
+        return None
+    return {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
+        "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peak, "peak_kind": peak_kind,
+                     "unit": "GB/s per GPU", "frac": round(value / world / peak, 4), "traffic": None},
+        "curve": curve, "breakdown": breakdown,
+        "e2e": {"value": round(e2e_gbs, 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": (launches + (2 * layers * len(W_BITS))) * args.steps,
+        "clocks": clocks,
+    }
 
 
 # --------------------------------------------------------------------------------------------- CPU arms

@@ -110,7 +110,9 @@ int ap_matmul_kbit_splitk(const void* x, const void* qweight, int64_t plane_stri
  *     AP_ERR_SCRATCH_LIMIT (splits = 8 at M = 1 fits up to N = 63488); use fewer splits
  *     or the workspace variant.
  *   - The first call on a device looks the area's device address up and clears it on `stream`;
- *     make that first call before capturing `stream` into anything, like any other set-up work.
+ *     make that first call before capturing `stream` into anything, like any other set-up work,
+ *     and let it COMPLETE (synchronise its stream once) before any call on another stream or from
+ *     another host thread: the clear is ordered only on the first caller's stream.
  *   - All calls on a device share the one area and leave their partial sums in it; only the
  *     ticket counters are kept at zero.  Two such calls that can run at the same time on the GPU
  *     (different streams) would corrupt each other: serialise them.
@@ -170,8 +172,11 @@ int ap_gemm_kbit_splitk(const void* x, const void* qweight, int64_t plane_stride
  *                   buffer, the others the mapped peer buffers; same max_payload on all ranks
  *     status        optional device int, set to 1 if a wait ran out (the output is then invalid;
  *                   nothing spins forever)
- *   All ranks must issue the same sequence of calls with the same counts.  Nothing is allocated
- *   or synchronised; the call can be captured in a CUDA graph and replayed.
+ *   All ranks must issue the same sequence of calls, call by call with the same count on every
+ *   rank; the counts of consecutive calls may differ freely (the inbox generation is taken from a
+ *   per-call counter, not from the call's size).  Calls of one communication buffer must be
+ *   stream-ordered on each rank.  Nothing is allocated or synchronised; the call can be captured
+ *   in a CUDA graph and replayed.
  */
 size_t ap_comm_buffer_bytes(size_t max_payload_bytes);
 int ap_comm_alloc(size_t bytes, void** ptr);

@@ -112,19 +112,29 @@ def algorithmic_bytes_gemv(M: int, N: int, K: int, w_bits: int) -> int:
 
 
 # --------------------------------------------------------------------------- C oracle
+def reference_root():
+    """Where a checkout of the reference project lies, or None: the ``REF_ROOT`` environment variable,
+    else a directory named ``reference`` beside this repository."""
+    cand = os.environ.get("REF_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "any_precision", "modules", "kernels")) else None
+
+
 def build(force: bool = False) -> None:
     """Compile ``liboracle.so`` (and ``_ref/`` when the reference tree is present)."""
     so = os.path.join(_HERE, "liboracle.so")
     src = os.path.join(_HERE, "anyprec_oracle.c")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
         subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
+    ref = reference_root()
+    if ref is None:
+        return                      # the checkers built from the reference's sources travel prebuilt
     ref_so = os.path.join(_HERE, "_ref", "libref_dequant.so")
     if force or not os.path.exists(ref_so):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, f"REF_ROOT={ref}", "ref"], check=True, capture_output=True)
     shim = os.path.join(_HERE, "ref_cuda_shim.cu")
     cuda_so = os.path.join(_HERE, "_ref", "libref_cuda.so")
     if force or not os.path.exists(cuda_so) or os.path.getmtime(cuda_so) < os.path.getmtime(shim):
-        subprocess.run(["make", "-C", _HERE, "refcuda"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, f"REF_ROOT={ref}", "refcuda"], check=True, capture_output=True)
 
 
 def usable_cpus() -> int:

@@ -86,11 +86,12 @@ def run_reference_packer(refpack, codes: np.ndarray, luts: dict) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="root of a checkout of the reference project (SNU-ARC/any-precision-llm)")
     args = ap.parse_args()
 
     from oracle import oracle
 
+    os.environ["REF_ROOT"] = args.ref
     oracle.build()
     if oracle.reflib() is None:
         raise SystemExit("oracle/_ref/libref_dequant.so missing: run `make -C oracle ref` first")

@@ -13,16 +13,25 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+# element counts of consecutive calls: 8 halfs per 16-byte vector, 512 vectors per block
+MIXED_COUNTS = (8, 4112, 8192, 8, 65536, 4112, 8, 8200, 4104, 65536, 16, 12304, 8192, 4112)
+
+
 def test_single_rank_roundtrip_and_graph_replay():
     from anyprec_b200.comm import OneShotAllReduce
     dev = torch.device("cuda", 0)
-    ar = OneShotAllReduce(64 * 1024, dev)
+    ar = OneShotAllReduce(128 * 1024, dev)
     gen = torch.Generator(device=dev).manual_seed(5)
     for n in (8, 4096, 8192, 32768):
         for _ in range(3):                                   # odd count: both generations get used
             x = torch.randn(n, device=dev, generator=gen).to(torch.float16)
             y = ar(x.clone())
             assert torch.equal(y, x)
+    # sizes whose block counts change from call to call (1, 2, 2, 1, 16, 2, 1, 64 blocks ...): the inbox
+    # generation must follow the call, not the block
+    for n in MIXED_COUNTS:
+        x = torch.randn(n, device=dev, generator=gen).to(torch.float16)
+        assert torch.equal(ar(x.clone()), x), n
     x = torch.randn(8192, device=dev, generator=gen).to(torch.float16)
     out = torch.empty_like(x)
     s = torch.cuda.Stream()
@@ -39,7 +48,7 @@ def test_single_rank_roundtrip_and_graph_replay():
         assert torch.equal(out, x)
     assert not ar.wait_expired()
     with pytest.raises(RuntimeError):
-        ar(torch.zeros(64 * 1024, device=dev, dtype=torch.float16))      # 128 KB payload > 64 KB
+        ar(torch.zeros(128 * 1024, device=dev, dtype=torch.float16))     # 256 KB payload > 128 KB
     ar.close()
 
 
@@ -67,6 +76,24 @@ def _rank_main(rank, world, port, result):
                 want += xs[r].float()                         # rank order, fp32: what the kernel does
             got = ar(xs[rank].to(dev)).cpu()
             ok = ok and torch.equal(got, want.to(torch.float16))
+        # Calls of changing size queued back to back with no host synchronisation in between (a rank can
+        # run a call ahead of another): results are compared only after the whole sequence.
+        seq = MIXED_COUNTS * 3
+        ins, wants = [], []
+        for it, n in enumerate(seq):
+            xs = [torch.randn(n, generator=torch.Generator().manual_seed(7000 + 10 * it + r)).to(torch.float16)
+                  for r in range(world)]
+            want = torch.zeros(n, dtype=torch.float32)
+            for r in range(world):
+                want += xs[r].float()
+            ins.append(xs[rank].to(dev))
+            wants.append(want.to(torch.float16))
+        torch.cuda.synchronize()
+        dist.barrier()
+        outs = [ar(t, out=torch.empty_like(t)) for t in ins]
+        torch.cuda.synchronize()
+        for got, want in zip(outs, wants):
+            ok = ok and torch.equal(got.cpu(), want)
         # replayed graph: the sequence numbers live on the device
         x = torch.full((8192,), float(rank + 1), device=dev, dtype=torch.float16)
         out = torch.empty_like(x)

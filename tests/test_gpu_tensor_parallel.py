@@ -1,0 +1,136 @@
+"""A sharded layer on real GPUs equals the unsharded layer.
+
+Two child processes, one GPU each: every rank shards the same seeded layer with
+``tensor_parallel.shard_linear`` (column-parallel views, row-parallel word slices and, for
+K = 7168 over two ranks, re-packed 3584-wide shards whose last group is partial), runs
+``any_precision_ext.matmul_kbit`` on its shard, and the row-parallel partial sums go through
+``comm.OneShotAllReduce``.  The result is compared with the unsharded ``matmul_kbit`` on the
+same GPU and with the CPU oracle, under the decode kernel's tolerance.  Skipped below two GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_layer
+
+pytestmark = pytest.mark.gpu
+
+MAX_REL = 1e-2
+REL_FLOOR = 0.05
+MEAN_ABS = 1e-3
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _close(y, ref):
+    y, ref = np.asarray(y, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    err = np.abs(y - ref)
+    denom = np.maximum(np.abs(ref), REL_FLOOR * np.abs(ref).max())
+    return bool((err / denom).max() <= MAX_REL and err.mean() <= MEAN_ABS)
+
+
+def _rank_main(rank, world, port, result):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import any_precision_ext as ext
+        from anyprec_b200 import packing, tensor_parallel as tp
+        from anyprec_b200.comm import OneShotAllReduce
+        from oracle import oracle
+        ar = OneShotAllReduce(8 * 512 * 2, dev)
+        ok, notes = True, []
+        # (N, K): plain row shards (K/2 a multiple of 1024), re-packed row shards (7168 -> 3584)
+        for N, K in ((256, 4096), (512, 7168)):
+            codes, luts_np = make_layer(N, K, seed=N + K)
+            qn = oracle.pack(codes)
+            q = torch.from_numpy(qn).to(dev)
+            luts = {w: torch.from_numpy(l).to(dev) for w, l in luts_np.items()}
+            for M in (1, 8):
+                xn = np.random.default_rng(K + M).normal(size=(M, K)).astype(np.float16)
+                x = torch.from_numpy(xn).to(dev)
+                for w in (3, 4, 8):
+                    ref = oracle.c_matmul(xn, qn, luts_np[w], w)
+                    full = ext.matmul_kbit(x, q, luts[w], w)
+                    # column-parallel: each rank's slice of the features, gathered on the host
+                    col = tp.shard_linear(q, luts, "col", rank, world)
+                    y_local = tp.shard_forward(x, col, w, ext.matmul_kbit).cpu()
+                    parts = [torch.empty_like(y_local) for _ in range(world)]
+                    dist.all_gather(parts, y_local)
+                    y_col = torch.cat(parts, dim=1)
+                    good = torch.equal(y_col, full.cpu()) and _close(y_col.numpy(), ref)
+                    # row-parallel: partial sums over the rank's K range, summed by the one-shot kernel
+                    row = tp.shard_linear(q, luts, "row", rank, world)
+                    k0, k1 = row.k_range
+                    y_row = tp.shard_forward(x[:, k0:k1].contiguous(), row, w, ext.matmul_kbit, allreduce=ar).cpu()
+                    good = good and _close(y_row.numpy(), ref) and _close(y_row.numpy(), full.cpu().numpy())
+                    if K == 7168:
+                        good = good and row.repacked and row.in_features == 3584
+                    if not good:
+                        notes.append((N, K, M, w))
+                    ok = ok and good
+        ok = ok and not ar.wait_expired() and not ext.take_wait_expired()
+        ar.close()
+        result[rank] = (ok, notes)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_layer_equals_unsharded_on_two_gpus():
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    result = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank did not finish")
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert all(result.get(r, (False, None))[0] for r in range(world)), dict(result)
+
+
+def test_sharded_layer_equals_unsharded_one_gpu_emulation():
+    """The same composition with both ranks' shards run one after the other on one GPU (the sum of
+    the row-parallel partials taken in fp32 on the host): covers shard_linear + matmul_kbit on
+    re-packed shards where only one GPU is there."""
+    import any_precision_ext as ext
+    from anyprec_b200 import tensor_parallel as tp
+    from oracle import oracle
+    dev = torch.device("cuda", 0)
+    world = 2
+    for N, K in ((256, 4096), (512, 7168)):
+        codes, luts_np = make_layer(N, K, seed=N + K)
+        qn = oracle.pack(codes)
+        q = torch.from_numpy(qn).to(dev)
+        luts = {w: torch.from_numpy(l).to(dev) for w, l in luts_np.items()}
+        xn = np.random.default_rng(K).normal(size=(3, K)).astype(np.float16)
+        x = torch.from_numpy(xn).to(dev)
+        for w in (3, 5, 8):
+            ref = oracle.c_matmul(xn, qn, luts_np[w], w)
+            cols, partial = [], torch.zeros((3, N), dtype=torch.float32, device=dev)
+            for rank in range(world):
+                col = tp.shard_linear(q, luts, "col", rank, world)
+                cols.append(ext.matmul_kbit(x, col.qweight, col.luts[w], w))
+                row = tp.shard_linear(q, luts, "row", rank, world)
+                k0, k1 = row.k_range
+                partial += ext.matmul_kbit(x[:, k0:k1].contiguous(), row.qweight, row.luts[w], w).float()
+                if K == 7168:
+                    assert row.repacked and row.in_features == 3584
+            assert _close(torch.cat(cols, dim=1).cpu().numpy(), ref), (N, K, w, "col")
+            assert _close(partial.cpu().numpy(), ref), (N, K, w, "row")

@@ -76,7 +76,7 @@ def test_noalloc_matches_workspace_variant_twice(lib, N, K, M, w, splits):
 def test_noalloc_refuses_what_does_not_fit(lib):
     cap = lib.ap_builtin_scratch_bytes()
     assert cap == 2 * 1024 * 1024
-    N, K, M, w = 70000 // 16 * 16, 128, 1, 3                       # 8 splits x 69 984 floats > 2 MiB
+    N, K, M, w = 70000 // 16 * 16, 8192, 1, 3                      # 8 splits x 69 984 floats > 2 MiB
     x, q, lut = _operands(N, K, M, w, seed=1)
     out = torch.zeros((M, N), dtype=torch.float16, device="cuda")
     rc = lib.ap_matmul_kbit_splitk_noalloc(x.data_ptr(), q.data_ptr(), q.stride(0), lut.data_ptr(), out.data_ptr(),
@@ -86,6 +86,12 @@ def test_noalloc_refuses_what_does_not_fit(lib):
     # one split needs no scratch at all and is always accepted
     rc = lib.ap_matmul_kbit_splitk_noalloc(x.data_ptr(), q.data_ptr(), q.stride(0), lut.data_ptr(), out.data_ptr(),
                                            M, N, K, w, 1, None)
+    assert rc == 0
+    # a request for more ranges than the row has 1024-weight groups is judged by what will run: K = 128
+    # has one group, so nothing is split and nothing is refused
+    x2, q2, lut2 = _operands(N, 128, M, w, seed=2)
+    rc = lib.ap_matmul_kbit_splitk_noalloc(x2.data_ptr(), q2.data_ptr(), q2.stride(0), lut2.data_ptr(), out.data_ptr(),
+                                           M, N, 128, w, 8, None)
     assert rc == 0
     torch.cuda.synchronize()
 
