@@ -1,0 +1,338 @@
+"""A minimal Llama-style decoder over ``AnyPrecisionLinear`` layers, for decode-rate measurements
+and for running packed checkpoints without Hugging Face ``transformers`` or ``accelerate``.
+
+The reference wraps the stock Hugging Face model and swaps its linears
+(any_precision/modules/AnyPrecisionForCausalLM.py:29-86); precision is selected per call with
+``forward(..., precision=)`` / ``generate(..., precision=)`` (:88-111) or ``set_precision`` (:171-174),
+and its ``fuse_layers`` is a stub (:186-190).  This class keeps that calling convention
+(``set_precision``, ``generate(input_ids, max_new_tokens, precision=)``) and does the fusion the
+reference leaves open:
+
+* q, k and v are one ``AnyPrecisionLinear`` (rows stacked, ``AnyPrecisionLinear.fuse``), gate and up
+  likewise, so a decoder layer issues four any-precision launches;
+* residual add + RMSNorm, rotary embedding + KV-cache write and SiLU * up are one small kernel each
+  (``ap_add_rmsnorm``, ``ap_rope_cache``, ``ap_silu_mul``);
+* a decode step reads its position from device memory, so one CUDA graph per precision is captured
+  once and replayed for every generated token.
+
+Attention over the static KV cache is ``ap_decode_attention`` for a decode step (one query per sequence,
+grouped-query heads, fp32 softmax) and ``torch.nn.functional.scaled_dot_product_attention`` for the
+prompt; ``lm_head`` and the embeddings stay fp16, as in the reference (only the modules its
+architecture files name are quantised, any_precision/analyzer/architectures/llama.yaml:5-12).
+Greedy sampling only; batch size fixed at construction.
+"""
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+import math
+
+import torch
+import torch.nn.functional as F
+
+import any_precision_ext as _ext
+
+from .modules.AnyPrecisionLinear import AnyPrecisionLinear
+
+__all__ = ["LlamaSpec", "AnyPrecisionLlama"]
+
+
+@dataclasses.dataclass
+class LlamaSpec:
+    hidden: int
+    heads: int
+    kv_heads: int
+    ffn: int
+    layers: int
+    vocab: int
+    head_dim: int = 0
+    rms_eps: float = 1e-5
+    rope_theta: float = 10000.0
+
+    def __post_init__(self):
+        if not self.head_dim:
+            self.head_dim = self.hidden // self.heads
+
+    @classmethod
+    def llama2_7b(cls):
+        return cls(hidden=4096, heads=32, kv_heads=32, ffn=11008, layers=32, vocab=32000)
+
+    @classmethod
+    def from_hf_config(cls, cfg: dict):
+        return cls(hidden=cfg["hidden_size"], heads=cfg["num_attention_heads"],
+                   kv_heads=cfg.get("num_key_value_heads", cfg["num_attention_heads"]), ffn=cfg["intermediate_size"],
+                   layers=cfg["num_hidden_layers"], vocab=cfg["vocab_size"], head_dim=cfg.get("head_dim", 0) or 0,
+                   rms_eps=cfg.get("rms_norm_eps", 1e-5), rope_theta=cfg.get("rope_theta", 10000.0))
+
+
+def _ops():
+    lib = _ext.load_library()
+    if getattr(lib, "_decoder_ready", False):
+        return lib
+    vp, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    lib.ap_add_rmsnorm.restype = i
+    lib.ap_add_rmsnorm.argtypes = [vp, vp, vp, vp, i, i, f, vp]
+    lib.ap_rope_cache.restype = i
+    lib.ap_rope_cache.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, vp]
+    lib.ap_silu_mul.restype = i
+    lib.ap_silu_mul.argtypes = [vp, vp, i, i, vp]
+    lib.ap_decode_attention.restype = i
+    lib.ap_decode_attention.argtypes = [vp, i, vp, vp, vp, vp, i, i, i, i, i, f, i, vp, vp]
+    lib.ap_decode_attention_scratch_bytes.restype = ctypes.c_size_t
+    lib.ap_decode_attention_scratch_bytes.argtypes = [i, i, i, i]
+    lib._decoder_ready = True
+    return lib
+
+
+def _check(lib, rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what}: {lib.ap_strerror(rc).decode()}")
+
+
+class _Layer:
+    __slots__ = ("qkv", "o", "gate_up", "down", "in_norm", "post_norm", "k_cache", "v_cache")
+
+
+class AnyPrecisionLlama:
+    """``spec``: model dimensions.  ``layers``: per decoder layer a dict with the seven
+    ``AnyPrecisionLinear`` modules (keys ``q_proj, k_proj, v_proj, o_proj, gate_proj, up_proj,
+    down_proj``) and the two norm weights (``input_layernorm``, ``post_attention_layernorm``)."""
+
+    def __init__(self, spec: LlamaSpec, layers, embed: torch.Tensor, final_norm: torch.Tensor, lm_head: torch.Tensor,
+                 device, batch: int = 1, max_seq: int = 1024):
+        self.spec, self.batch, self.max_seq = spec, batch, max_seq
+        self.device = torch.device(device)
+        self.lib = _ops()
+        dev, s = self.device, spec
+        self.embed = embed.to(dev, torch.float16).contiguous()
+        self.final_norm = final_norm.to(dev, torch.float16).contiguous()
+        self.lm_head = lm_head.to(dev, torch.float16).contiguous()
+        self.layers = []
+        for src in layers:
+            L = _Layer()
+            L.qkv = AnyPrecisionLinear.fuse([src["q_proj"].to(dev), src["k_proj"].to(dev), src["v_proj"].to(dev)])
+            L.o = src["o_proj"].to(dev)
+            L.gate_up = AnyPrecisionLinear.fuse([src["gate_proj"].to(dev), src["up_proj"].to(dev)])
+            L.down = src["down_proj"].to(dev)
+            L.in_norm = src["input_layernorm"].to(dev, torch.float16).contiguous()
+            L.post_norm = src["post_attention_layernorm"].to(dev, torch.float16).contiguous()
+            L.k_cache = torch.zeros((batch, s.kv_heads, max_seq, s.head_dim), dtype=torch.float16, device=dev)
+            L.v_cache = torch.zeros_like(L.k_cache)
+            self.layers.append(L)
+        self.precisions = list(self.layers[0].o.precisions)
+        self.precision = max(self.precisions)
+        # rotary tables: [max_seq][cos(head_dim / 2) | sin(head_dim / 2)] in fp32
+        inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float64) / s.head_dim))
+        ang = torch.arange(max_seq, dtype=torch.float64)[:, None] * inv[None, :]
+        self.cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).to(torch.float32).to(dev).contiguous()
+        # decode state, all on the device so that a captured step can be replayed
+        self.pos = torch.zeros(batch, dtype=torch.int32, device=dev)          # position of the token being processed
+        self.tok = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self.h = torch.empty((batch, s.hidden), dtype=torch.float16, device=dev)
+        self.y = torch.empty_like(self.h)
+        self.act = torch.empty((batch, s.ffn), dtype=torch.float16, device=dev)
+        self.attn = torch.empty((batch, s.heads * s.head_dim), dtype=torch.float16, device=dev)
+        # a decode step has few heads: cut each head's cached positions over enough blocks for about two per SM
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.attn_splits = max(1, min(16, (2 * sms) // (batch * s.heads), max_seq // 64))
+        self.attn_scratch = None
+        if self.attn_splits > 1:
+            nbytes = self.lib.ap_decode_attention_scratch_bytes(batch, s.heads, s.head_dim, self.attn_splits)
+            self.attn_scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        self._graphs = {}
+        self._side = None                                   # the stream decode graphs are captured and replayed on
+
+    # ------------------------------------------------------------------------------------ construction
+    @classmethod
+    def random_init(cls, spec: LlamaSpec, device, supported_bits=(3, 4, 5, 6, 7, 8), seed: int = 0, batch: int = 1,
+                    max_seq: int = 1024):
+        """Random weights of the right architecture: uniform parent codes (drawn directly as random
+        bitplanes), per-row sorted N(0, 0.02) tables, N(0, 0.02) fp16 embeddings and ``lm_head``, unit norms."""
+        from . import packing
+        dev = torch.device(device)
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        bits = list(supported_bits)
+        shapes = {"q_proj": (spec.heads * spec.head_dim, spec.hidden), "k_proj": (spec.kv_heads * spec.head_dim, spec.hidden),
+                  "v_proj": (spec.kv_heads * spec.head_dim, spec.hidden), "o_proj": (spec.hidden, spec.heads * spec.head_dim),
+                  "gate_proj": (spec.ffn, spec.hidden), "up_proj": (spec.ffn, spec.hidden), "down_proj": (spec.hidden, spec.ffn)}
+        layers = []
+        for _ in range(spec.layers):
+            d = {}
+            for name, (N, K) in shapes.items():
+                m = AnyPrecisionLinear(K, N, bits, bias=False, device="meta")
+                m.qweight = packing.random_qweight(max(bits), N, K, device=dev, generator=gen)
+                for b in bits:
+                    setattr(m, f"lut{b}", packing.random_lut(N, b, device=dev, generator=gen))
+                d[name] = m
+            d["input_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
+            d["post_attention_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
+            layers.append(d)
+        embed = (torch.randn((spec.vocab, spec.hidden), device=dev, generator=gen) * 0.02).half()
+        head = (torch.randn((spec.vocab, spec.hidden), device=dev, generator=gen) * 0.02).half()
+        return cls(spec, layers, embed, torch.ones(spec.hidden, dtype=torch.float16, device=dev), head, dev, batch, max_seq)
+
+    @classmethod
+    def from_packed(cls, path: str, device, precisions=None, batch: int = 1, max_seq: int = 1024):
+        """Build the model from a packed checkpoint directory written by the reference's packer (Llama
+        architecture: ``arch_config`` must name the seven Llama projections)."""
+        from . import checkpoint
+        config, linears, rest = checkpoint.load_linears(path, precisions=precisions, device=None)
+        arch = config["anyprec"]["arch_config"]
+        spec = LlamaSpec.from_hf_config(config)
+        prefix = f"{arch['model_name']}.{arch['layers_name']}"
+        layers = []
+        for L in range(spec.layers):
+            d = {}
+            for full in arch["module_names"]:
+                d[full.split(".")[-1]] = linears[f"{prefix}.{L}.{full}"]
+            missing = {"q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"} - set(d)
+            if missing:
+                raise ValueError(f"layer {L}: the checkpoint does not hold {sorted(missing)} (not a Llama-style model?)")
+            d["input_layernorm"] = rest[f"{prefix}.{L}.input_layernorm.weight"]
+            d["post_attention_layernorm"] = rest[f"{prefix}.{L}.post_attention_layernorm.weight"]
+            layers.append(d)
+        embed = rest[f"{arch['model_name']}.embed_tokens.weight"]
+        head = rest.get("lm_head.weight", embed)
+        return cls(spec, layers, embed, rest[f"{arch['model_name']}.norm.weight"], head, device, batch, max_seq)
+
+    # ------------------------------------------------------------------------------------ precision
+    def set_precision(self, precision: int):
+        if precision not in self.precisions:
+            raise RuntimeError(f"{self.precisions}-bit precisions are supported but {precision}-bit was specified.")
+        for L in self.layers:
+            for m in (L.qkv, L.o, L.gate_up, L.down):
+                m.set_precision(precision)
+        self.precision = precision
+
+    # ------------------------------------------------------------------------------------ building blocks
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _add_rmsnorm(self, h, delta, weight, y):
+        rows = h.shape[0]
+        _check(self.lib, self.lib.ap_add_rmsnorm(h.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                                 weight.data_ptr(), y.data_ptr(), rows, self.spec.hidden,
+                                                 self.spec.rms_eps, self._stream()), "ap_add_rmsnorm")
+
+    def _layer_tail(self, L, h, y, attn):
+        """o_proj, residual + norm, gate/up, SiLU * up, down; returns the MLP output (the caller adds it)."""
+        s = self.spec
+        o = L.o(attn)
+        self._add_rmsnorm(h, o, L.post_norm, y)
+        gu = L.gate_up(y)
+        rows = gu.shape[0]
+        act = self.act[:rows] if rows <= self.batch else torch.empty((rows, s.ffn), dtype=torch.float16, device=self.device)
+        _check(self.lib, self.lib.ap_silu_mul(gu.data_ptr(), act.data_ptr(), rows, s.ffn, self._stream()), "ap_silu_mul")
+        return L.down(act)
+
+    # ------------------------------------------------------------------------------------ prefill
+    @torch.inference_mode()
+    def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Run the prompt ``[batch, T]`` through the model, fill the KV caches for positions 0..T-1 and
+        return the logits of the last position ``[batch, vocab]``.  The linears see ``batch * T`` rows,
+        i.e. their prefill path."""
+        s, B = self.spec, self.batch
+        if input_ids.shape[0] != B:
+            raise ValueError(f"the model was built for batch {B}")
+        T = input_ids.shape[1]
+        if T > self.max_seq:
+            raise ValueError("prompt longer than the KV cache")
+        with torch.cuda.device(self.device):
+            ids = input_ids.to(self.device)
+            h = self.embed[ids].reshape(B * T, s.hidden).contiguous()
+            y = torch.empty_like(h)
+            pos = torch.arange(T, device=self.device, dtype=torch.int32).repeat(B)
+            mlp = None
+            for L in self.layers:
+                self._add_rmsnorm(h, mlp, L.in_norm, y)
+                qkv = L.qkv(y)                                             # [B*T, (H + 2 KV) * D]
+                _check(self.lib, self.lib.ap_rope_cache(qkv.data_ptr(), self.cos_sin.data_ptr(), pos.data_ptr(),
+                                                        L.k_cache.data_ptr(), L.v_cache.data_ptr(), B * T, T, s.heads,
+                                                        s.kv_heads, s.head_dim, self.max_seq, self._stream()), "ap_rope_cache")
+                q = qkv[:, :s.heads * s.head_dim].reshape(B, T, s.heads, s.head_dim).transpose(1, 2)   # [B, H, T, D]
+                k, v = L.k_cache[:, :, :T], L.v_cache[:, :, :T]
+                attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=s.kv_heads != s.heads)
+                attn = attn.transpose(1, 2).reshape(B * T, s.heads * s.head_dim)
+                mlp = self._layer_tail(L, h, y, attn)
+            self._add_rmsnorm(h, mlp, self.final_norm, y)
+            last = y.view(B, T, s.hidden)[:, -1]
+            self.pos.fill_(T)
+            return last @ self.lm_head.T
+
+    # ------------------------------------------------------------------------------------ decode
+    def _decode_step(self):
+        """One token per sequence: reads ``self.tok`` and ``self.pos``, writes the next token to ``self.tok``
+        and advances ``self.pos``.  Everything it touches lives on the device (graph-replayable)."""
+        s, B = self.spec, self.batch
+        self.h.copy_(self.embed[self.tok])
+        mlp = None
+        for L in self.layers:
+            self._add_rmsnorm(self.h, mlp, L.in_norm, self.y)
+            qkv = L.qkv(self.y)                                              # decode kernel: B <= 8 rows
+            _check(self.lib, self.lib.ap_rope_cache(qkv.data_ptr(), self.cos_sin.data_ptr(), self.pos.data_ptr(),
+                                                    L.k_cache.data_ptr(), L.v_cache.data_ptr(), B, 1, s.heads, s.kv_heads,
+                                                    s.head_dim, self.max_seq, self._stream()), "ap_rope_cache")
+            _check(self.lib, self.lib.ap_decode_attention(qkv.data_ptr(), qkv.shape[1], L.k_cache.data_ptr(),
+                                                          L.v_cache.data_ptr(), self.pos.data_ptr(), self.attn.data_ptr(), B,
+                                                          s.heads, s.kv_heads, s.head_dim, self.max_seq,
+                                                          1.0 / math.sqrt(s.head_dim), self.attn_splits,
+                                                          self.attn_scratch.data_ptr() if self.attn_scratch is not None else None,
+                                                          self._stream()), "ap_decode_attention")
+            mlp = self._layer_tail(L, self.h, self.y, self.attn)
+        self._add_rmsnorm(self.h, mlp, self.final_norm, self.y)
+        logits = self.y @ self.lm_head.T
+        self.tok.copy_(logits.argmax(dim=-1))
+        self.pos.add_(1)
+
+    def _graph(self, precision):
+        """The captured decode step of ``precision``.  Must be called on the side stream the graphs live on
+        (``generate`` does): the split-K scratch of the linears belongs to the stream that captures."""
+        g = self._graphs.get(precision)
+        if g is None:
+            stream = torch.cuda.current_stream(self.device)
+            _ext.reserve_workspace(self.device)
+            pos0, tok0 = self.pos.clone(), self.tok.clone()
+            self._decode_step()                                  # warm-up outside the capture (allocations, tensor maps)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                self._decode_step()
+            self.pos.copy_(pos0)
+            self.tok.copy_(tok0)
+            self._graphs[precision] = g
+        return g
+
+    @torch.inference_mode()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int, precision: int | None = None,
+                 use_graph: bool = True) -> torch.Tensor:
+        """Greedy generation: ``[batch, T]`` prompt -> ``[batch, T + max_new_tokens]``.  ``precision``
+        applies to this call only, as in the reference's ``generate`` (AnyPrecisionForCausalLM.py:99-111)."""
+        prev = self.precision
+        if precision is not None:
+            self.set_precision(precision)
+        try:
+            with torch.cuda.device(self.device):
+                T = input_ids.shape[1]
+                if T + max_new_tokens > self.max_seq:
+                    raise ValueError("prompt + new tokens exceed the KV cache")
+                logits = self.prefill(input_ids)
+                out = [logits.argmax(dim=-1)]
+                self.tok.copy_(out[0])
+                if use_graph and max_new_tokens > 1:
+                    if self._side is None:
+                        self._side = torch.cuda.Stream(self.device)
+                    stream = self._side
+                    stream.wait_stream(torch.cuda.current_stream(self.device))
+                    with torch.cuda.stream(stream):
+                        g = self._graph(self.precision)
+                        for _ in range(max_new_tokens - 1):
+                            g.replay()
+                            out.append(self.tok.clone())
+                    torch.cuda.current_stream(self.device).wait_stream(stream)
+                else:
+                    for _ in range(max_new_tokens - 1):
+                        self._decode_step()
+                        out.append(self.tok.clone())
+                return torch.cat([input_ids.to(self.device), torch.stack(out, dim=1)], dim=1)
+        finally:
+            self.set_precision(prev)

@@ -44,11 +44,39 @@ def element_map(K: int, device=None) -> torch.Tensor:
     return _element_map_cpu(K).to(device) if device is not None else _element_map_cpu(K)
 
 
+def _lib():
+    import ctypes
+
+    import any_precision_ext
+    lib = any_precision_ext.load_library()
+    if not getattr(lib, "_pack_ready", False):
+        vp, i, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+        lib.ap_pack_codes.restype = i
+        lib.ap_pack_codes.argtypes = [vp, vp, i64, i, i, i, vp]
+        lib.ap_unpack_codes.restype = i
+        lib.ap_unpack_codes.argtypes = [vp, i64, vp, i, i, i, vp]
+        lib._pack_ready = True
+    return lib
+
+
 def pack_codes(codes: torch.Tensor, parent_bits: int = 8) -> torch.Tensor:
-    """uint8 codes ``[N, K]`` (values < 2**parent_bits) -> int32 ``[parent_bits, N, K/32]``."""
+    """uint8 codes ``[N, K]`` (values < 2**parent_bits) -> int32 ``[parent_bits, N, K/32]``.  On a CUDA tensor
+    this is one kernel (``ap_pack_codes``); on the CPU the same map written with torch ops."""
     if codes.dtype != torch.uint8 or codes.dim() != 2:
         raise TypeError("codes must be a uint8 [N, K] tensor")
     N, K = codes.shape
+    if codes.is_cuda:
+        if K % 32 or K <= 0:
+            raise ValueError("K must be a positive multiple of 32")
+        codes = codes.contiguous()
+        q = torch.empty((parent_bits, N, K // 32), dtype=torch.int32, device=codes.device)
+        lib = _lib()
+        with torch.cuda.device(codes.device):
+            rc = lib.ap_pack_codes(codes.data_ptr(), q.data_ptr(), N * (K // 32), N, K, parent_bits,
+                                   torch.cuda.current_stream(codes.device).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"ap_pack_codes: {lib.ap_strerror(rc).decode()}")
+        return q
     kmap = element_map(K, codes.device)
     perm = codes[:, kmap].to(torch.int32).view(N, K // 32, 32)     # bit 31 first
     shifts = torch.arange(31, -1, -1, device=codes.device, dtype=torch.int64)
@@ -69,6 +97,15 @@ def unpack_codes(qweight: torch.Tensor, w_bits: int) -> torch.Tensor:
     if not 1 <= w_bits <= planes:
         raise ValueError("w_bits out of range")
     K = words * 32
+    if qweight.is_cuda and qweight.stride(2) == 1 and qweight.stride(1) == words:
+        codes = torch.empty((N, K), dtype=torch.uint8, device=qweight.device)
+        lib = _lib()
+        with torch.cuda.device(qweight.device):
+            rc = lib.ap_unpack_codes(qweight.data_ptr(), qweight.stride(0) if planes > 1 else N * words, codes.data_ptr(),
+                                     N, K, w_bits, torch.cuda.current_stream(qweight.device).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"ap_unpack_codes: {lib.ap_strerror(rc).decode()}")
+        return codes
     kmap = element_map(K, qweight.device)
     shifts = torch.arange(31, -1, -1, device=qweight.device, dtype=torch.int32)
     codes_perm = torch.zeros((N, K), dtype=torch.int32, device=qweight.device)

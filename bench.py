@@ -396,6 +396,7 @@ def run_ours(args):
     prefill = prefill_figures(torch, ext, packing, device)
     # The tensor-parallel workload (Llama-2-70B layer set) on this one GPU: the anchor of the 1/2/4/8 curve.
     tp1 = tensor_parallel_figures(args, 0, 1, device, args.layers, full=False)
+    decoder = decoder_figures(args, device)
     cpu = cpu_baseline_sample(kind_pref="port", seconds_hint=15)
 
     line = {
@@ -409,6 +410,7 @@ def run_ours(args):
                              "note": "same weights, q+k+v and gate+up stacked by rows (packing.concat_rows)"},
         "prefill": prefill,
         "tp1_llama2_70b": tp1,
+        "decoder_llama2_7b": decoder,
         "per_w_bits_gbs": per_w,
         "per_w_bits_frac_of_measured_peak": {k: round(v / peak, 3) for k, v in per_w.items()},
         "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
@@ -430,6 +432,59 @@ def run_ours(args):
     return line
 
 
+
+
+# ------------------------------------------------------------------------------------- whole-model decode
+def decoder_figures(args, device):
+    """Decode rate of a whole random-init Llama-2-7B decoder whose linears are any-precision layers: a
+    512-token prompt of uniform random token ids, then 128 greedy steps at batch 1, for every w_bits.
+    `generate_tok_s` is the wall-clock method of the reference's demo (new tokens over the whole generate call,
+    prompt included, synchronised at both ends); `decode_tok_s` times the 127 replayed decode steps alone
+    with CUDA events.  `bound_tok_s` is what the measured HBM peak allows for the bytes a step must read
+    (planes, that precision's tables, fp16 lm_head; KV cache and activations not counted)."""
+    import torch
+
+    from anyprec_b200.decoder import AnyPrecisionLlama, LlamaSpec
+
+    spec = LlamaSpec.llama2_7b()
+    prompt, new = 512, 128
+    model = AnyPrecisionLlama.random_init(spec, device, seed=2000, batch=1, max_seq=prompt + new)
+    ids = torch.randint(0, spec.vocab, (1, prompt), generator=torch.Generator().manual_seed(2))
+    peak, _ = measured_peak_gbs()
+    per_layer = [(spec.heads * spec.head_dim + 2 * spec.kv_heads * spec.head_dim, spec.hidden), (spec.hidden, spec.hidden),
+                 (2 * spec.ffn, spec.hidden), (spec.hidden, spec.ffn)]
+    out = {}
+    for w in W_BITS:
+        model.generate(ids, 4, precision=w)                                   # captures this precision's decode graph
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        toks = model.generate(ids, new, precision=w)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        assert toks.shape == (1, prompt + new)
+        # the decode steps alone
+        model.set_precision(w)
+        logits = model.prefill(ids)
+        model.tok.copy_(logits.argmax(-1))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(model._side):
+            g = model._graph(w)                                               # cached by the generate calls above
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(new - 1):
+                g.replay()
+            b.record()
+        torch.cuda.synchronize()
+        step_ms = a.elapsed_time(b) / (new - 1)
+        step_bytes = spec.layers * sum(N * K * w // 8 + N * (1 << w) * 2 for N, K in per_layer) + spec.vocab * spec.hidden * 2
+        out[str(w)] = {"generate_tok_s": round(new / wall, 1), "decode_tok_s": round(1e3 / step_ms, 1),
+                       "decode_ms_per_token": round(step_ms, 4), "bound_tok_s": round(peak * 1e9 / step_bytes, 1),
+                       "frac_of_bound": round(1e3 / step_ms / (peak * 1e9 / step_bytes), 3)}
+    del model
+    torch.cuda.empty_cache()
+    return {"model": "random-init Llama-2-7B decoder (32 layers, hidden 4096, 32 heads, FFN 11008, vocab 32000), every "
+                     "linear an 8-bit-parent any-precision layer; q+k+v and gate+up stacked; one CUDA graph per precision",
+            "prompt_tokens": prompt, "new_tokens": new, "batch": 1, "per_w_bits": out}
 
 # ----------------------------------------------------------------------------- tensor-parallel workload
 def tensor_parallel_figures(args, rank, world, device, layers, full):

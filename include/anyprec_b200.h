@@ -188,6 +188,50 @@ const char* ap_comm_last_error(void);
 int ap_allreduce_oneshot(const void* src, void* out, int count, void* const* peer_buffers, int rank, int world,
                          size_t max_payload_bytes, int* status, void* stream);
 
+/*
+ * The packed format on the device.  ap_pack_codes replaces the bitplane loop and byte permutation of the
+ * reference's CPU packer (any_precision/quantization/pack.py:12-76,86-99): codes uint8 [N][K] (values below
+ * 2^parent_bits, rows 8-byte aligned: K % 32 == 0 and an 8-byte aligned base) -> qweight int32
+ * [parent_bits][N][K/32], plane 0 = MSB.  ap_unpack_codes is the inverse for the top w_bits planes
+ * (codes of precision w_bits); the reference has it only implicitly, in its kernels.  Used to build
+ * operands and to re-pack K-shards whose last group is partial.
+ */
+int ap_pack_codes(const void* codes, void* qweight, int64_t plane_stride, int N, int K, int parent_bits, void* stream);
+int ap_unpack_codes(const void* qweight, int64_t plane_stride, void* codes, int N, int K, int w_bits, void* stream);
+
+/*
+ * Element-wise operations between the linear layers of a Llama-style decoder step, so that a decode
+ * step is a few launches per layer.  No counterpart in the reference's kernels: the reference runs the
+ * stock Hugging Face decoder layer around its linears (any_precision/modules/AnyPrecisionForCausalLM.py:
+ * 54-60; its fuse_layers, :186-190, is a stub).  fp16 in and out, fp32 arithmetic, launched as
+ * programmatic dependents like the other kernels.
+ *   ap_add_rmsnorm  h[rows][hidden] += delta (delta may be NULL), then y = h * rsqrt(mean(h^2) + eps) * weight
+ *   ap_rope_cache   qkv[rows][(heads + 2 kv_heads) * head_dim] holds q | k | v of one token per row;
+ *                   q is rotated in place (pairs (i, i + head_dim/2)), rotated k and plain v are stored
+ *                   at position pos[row] of sequence row / rows_per_seq in k_cache / v_cache
+ *                   [sequences][kv_heads][max_seq][head_dim] (rows_per_seq = 1 for a decode step).
+ *                   cos_sin: fp32 [max_seq][head_dim] = cos(head_dim/2) | sin(head_dim/2) per position;
+ *                   pos: device int32[rows] (a row whose position is outside [0, max_seq) is skipped)
+ *   ap_silu_mul     y[rows][ffn] = silu(gate) * up for gate_up[rows][2 * ffn] = gate | up
+ *   ap_decode_attention  one query token per sequence: out[b][h][:] = softmax(q . K[0..pos[b]] * scale) V[0..pos[b]]
+ *                   with q = qkv[b * q_row_stride + h * head_dim ...] (the rotated q part of the q|k|v row),
+ *                   caches as in ap_rope_cache, grouped-query heads (heads % kv_heads == 0), head_dim 32, 64,
+ *                   128 or 256, out fp16 [sequences][heads * head_dim].  `splits` > 1 cuts every head's cached
+ *                   positions into that many ranges taken by different thread blocks (a decode step has few
+ *                   heads); it needs `scratch`: 16-byte aligned device memory of
+ *                   ap_decode_attention_scratch_bytes(...) bytes whose first sequences * heads ints are ticket
+ *                   counters, ZERO before the first call and left zero by every call
+ */
+int ap_add_rmsnorm(void* h, const void* delta, const void* weight, void* y, int rows, int hidden, float eps,
+                   void* stream);
+int ap_rope_cache(void* qkv, const void* cos_sin, const void* pos, void* k_cache, void* v_cache, int rows,
+                  int rows_per_seq, int heads, int kv_heads, int head_dim, int max_seq, void* stream);
+int ap_silu_mul(const void* gate_up, void* y, int rows, int ffn, void* stream);
+size_t ap_decode_attention_scratch_bytes(int sequences, int heads, int head_dim, int splits);
+int ap_decode_attention(const void* qkv, int q_row_stride, const void* k_cache, const void* v_cache, const void* pos,
+                        void* out, int sequences, int heads, int kv_heads, int head_dim, int max_seq, float scale,
+                        int splits, void* scratch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
