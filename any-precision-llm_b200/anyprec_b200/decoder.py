@@ -58,6 +58,10 @@ class LlamaSpec:
         return cls(hidden=4096, heads=32, kv_heads=32, ffn=11008, layers=32, vocab=32000)
 
     @classmethod
+    def llama2_70b(cls):
+        return cls(hidden=8192, heads=64, kv_heads=8, ffn=28672, layers=80, vocab=32000)
+
+    @classmethod
     def from_hf_config(cls, cfg: dict):
         return cls(hidden=cfg["hidden_size"], heads=cfg["num_attention_heads"],
                    kv_heads=cfg.get("num_key_value_heads", cfg["num_attention_heads"]), ffn=cfg["intermediate_size"],
@@ -89,55 +93,98 @@ def _check(lib, rc, what):
         raise RuntimeError(f"{what}: {lib.ap_strerror(rc).decode()}")
 
 
+def _shard_module(m: AnyPrecisionLinear, style: str, rank: int, world: int) -> AnyPrecisionLinear:
+    """This rank's shard of a layer as a module of its own: rows ``[n0, n1)`` for a column-parallel layer,
+    input columns ``[k0, k1)`` (re-packed when the shard's last group is partial) with the full tables for
+    a row-parallel one (``tensor_parallel.shard_linear``)."""
+    from .tensor_parallel import shard_linear
+    luts = {b: getattr(m, f"lut{b}") for b in m.supported_bits if hasattr(m, f"lut{b}")}
+    sh = shard_linear(m.qweight, luts, style, rank, world)
+    out = AnyPrecisionLinear(sh.in_features, sh.out_features, list(m.supported_bits), bias=False,
+                             precisions=list(m.precisions), device="meta")
+    out.qweight = sh.qweight.contiguous()
+    for b in m.supported_bits:
+        if b in sh.luts:
+            setattr(out, f"lut{b}", sh.luts[b].contiguous())
+        elif hasattr(out, f"lut{b}"):
+            delattr(out, f"lut{b}")
+    if m.bias is not None:
+        raise ValueError("sharding layers with a bias is not supported")
+    out.precision = m.precision
+    return out
+
+
 class _Layer:
     __slots__ = ("qkv", "o", "gate_up", "down", "in_norm", "post_norm", "k_cache", "v_cache")
 
 
 class AnyPrecisionLlama:
-    """``spec``: model dimensions.  ``layers``: per decoder layer a dict with the seven
-    ``AnyPrecisionLinear`` modules (keys ``q_proj, k_proj, v_proj, o_proj, gate_proj, up_proj,
-    down_proj``) and the two norm weights (``input_layernorm``, ``post_attention_layernorm``)."""
+    """``spec``: model dimensions.  ``layers``: an iterable giving, per decoder layer, a dict with the seven
+    ``AnyPrecisionLinear`` modules (keys ``q_proj, k_proj, v_proj, o_proj, gate_proj, up_proj, down_proj``;
+    ``qkv_proj`` / ``gate_up_proj`` may stand for the already stacked ones) and the two norm weights
+    (``input_layernorm``, ``post_attention_layernorm``).
+
+    Tensor parallelism (``tp_world`` > 1, one process per GPU, no counterpart in the reference): the layers
+    handed in are this rank's shards: q/k/v/gate/up hold ``heads / tp_world`` (``kv_heads / tp_world``)
+    heads and ``ffn / tp_world`` rows, o/down the matching input columns, tables of o/down and everything
+    unquantised replicated.  The outputs of o and down are summed over the ranks: by ``allreduce`` (a
+    ``comm.OneShotAllReduce``) in decode steps, by the process group for the prompt."""
 
     def __init__(self, spec: LlamaSpec, layers, embed: torch.Tensor, final_norm: torch.Tensor, lm_head: torch.Tensor,
-                 device, batch: int = 1, max_seq: int = 1024):
+                 device, batch: int = 1, max_seq: int = 1024, tp_world: int = 1, allreduce=None, group=None):
         self.spec, self.batch, self.max_seq = spec, batch, max_seq
         self.device = torch.device(device)
         self.lib = _ops()
         dev, s = self.device, spec
+        if tp_world < 1 or s.heads % tp_world or s.kv_heads % tp_world or s.ffn % tp_world:
+            raise ValueError("tp_world must divide heads, kv_heads and ffn")
+        self.tp_world, self.allreduce, self.group = tp_world, allreduce, group
+        self.heads, self.kv_heads = s.heads // tp_world, s.kv_heads // tp_world        # this rank's
+        self.ffn = s.ffn // tp_world
         self.embed = embed.to(dev, torch.float16).contiguous()
         self.final_norm = final_norm.to(dev, torch.float16).contiguous()
         self.lm_head = lm_head.to(dev, torch.float16).contiguous()
         self.layers = []
         for src in layers:
             L = _Layer()
-            L.qkv = AnyPrecisionLinear.fuse([src["q_proj"].to(dev), src["k_proj"].to(dev), src["v_proj"].to(dev)])
+            L.qkv = src["qkv_proj"].to(dev) if "qkv_proj" in src else \
+                AnyPrecisionLinear.fuse([src["q_proj"].to(dev), src["k_proj"].to(dev), src["v_proj"].to(dev)])
             L.o = src["o_proj"].to(dev)
-            L.gate_up = AnyPrecisionLinear.fuse([src["gate_proj"].to(dev), src["up_proj"].to(dev)])
+            L.gate_up = src["gate_up_proj"].to(dev) if "gate_up_proj" in src else \
+                AnyPrecisionLinear.fuse([src["gate_proj"].to(dev), src["up_proj"].to(dev)])
             L.down = src["down_proj"].to(dev)
+            if L.qkv.out_features != (self.heads + 2 * self.kv_heads) * s.head_dim or L.down.in_features != self.ffn:
+                raise ValueError("layer shapes do not match the model dimensions (and tp_world)")
             L.in_norm = src["input_layernorm"].to(dev, torch.float16).contiguous()
             L.post_norm = src["post_attention_layernorm"].to(dev, torch.float16).contiguous()
-            L.k_cache = torch.zeros((batch, s.kv_heads, max_seq, s.head_dim), dtype=torch.float16, device=dev)
-            L.v_cache = torch.zeros_like(L.k_cache)
             self.layers.append(L)
+            src.clear()                                      # the separate q/k/v, gate/up operands are not kept
         self.precisions = list(self.layers[0].o.precisions)
         self.precision = max(self.precisions)
         # rotary tables: [max_seq][cos(head_dim / 2) | sin(head_dim / 2)] in fp32
         inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float64) / s.head_dim))
         ang = torch.arange(max_seq, dtype=torch.float64)[:, None] * inv[None, :]
         self.cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).to(torch.float32).to(dev).contiguous()
-        # decode state, all on the device so that a captured step can be replayed
+        self._allocate_state()
+
+    def _allocate_state(self):
+        """KV caches and the decode step's buffers, all on the device so that a captured step can be replayed."""
+        dev, s, batch, max_seq = self.device, self.spec, self.batch, self.max_seq
+        for L in self.layers:
+            L.k_cache = torch.zeros((batch, self.kv_heads, max_seq, s.head_dim), dtype=torch.float16, device=dev)
+            L.v_cache = torch.zeros_like(L.k_cache)
         self.pos = torch.zeros(batch, dtype=torch.int32, device=dev)          # position of the token being processed
         self.tok = torch.zeros(batch, dtype=torch.int64, device=dev)
         self.h = torch.empty((batch, s.hidden), dtype=torch.float16, device=dev)
         self.y = torch.empty_like(self.h)
-        self.act = torch.empty((batch, s.ffn), dtype=torch.float16, device=dev)
-        self.attn = torch.empty((batch, s.heads * s.head_dim), dtype=torch.float16, device=dev)
+        self.act = torch.empty((batch, self.ffn), dtype=torch.float16, device=dev)
+        self.attn = torch.empty((batch, self.heads * s.head_dim), dtype=torch.float16, device=dev)
         # a decode step has few heads: cut each head's cached positions over enough blocks for about two per SM
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        self.attn_splits = max(1, min(16, (2 * sms) // (batch * s.heads), max_seq // 64))
+        self.attn_splits = max(1, min(16, (2 * sms) // (batch * self.heads), max_seq // 64))
         self.attn_scratch = None
         if self.attn_splits > 1:
-            nbytes = self.lib.ap_decode_attention_scratch_bytes(batch, s.heads, s.head_dim, self.attn_splits)
+            nbytes = self.lib.ap_decode_attention_scratch_bytes(batch, self.heads, s.head_dim, self.attn_splits)
             self.attn_scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         self._graphs = {}
         self._side = None                                   # the stream decode graphs are captured and replayed on
@@ -145,55 +192,93 @@ class AnyPrecisionLlama:
     # ------------------------------------------------------------------------------------ construction
     @classmethod
     def random_init(cls, spec: LlamaSpec, device, supported_bits=(3, 4, 5, 6, 7, 8), seed: int = 0, batch: int = 1,
-                    max_seq: int = 1024):
+                    max_seq: int = 1024, tp_rank: int = 0, tp_world: int = 1, allreduce=None, group=None):
         """Random weights of the right architecture: uniform parent codes (drawn directly as random
-        bitplanes), per-row sorted N(0, 0.02) tables, N(0, 0.02) fp16 embeddings and ``lm_head``, unit norms."""
+        bitplanes; q+k+v and gate+up as the stacked operands they end up as), per-row sorted N(0, 0.02)
+        tables, N(0, 0.02) fp16 embeddings and ``lm_head``, unit norms.  With ``tp_world`` > 1 every rank
+        draws its own shard; what is replicated (tables of o/down, embeddings, ``lm_head``) comes from a
+        generator seeded alike on all ranks."""
         from . import packing
         dev = torch.device(device)
-        gen = torch.Generator(device=dev).manual_seed(seed)
+        gen = torch.Generator(device=dev).manual_seed(seed * 1000 + 17 * tp_rank + 1)      # this rank's shards
+        common = torch.Generator(device=dev).manual_seed(seed * 1000)                      # replicated tensors
         bits = list(supported_bits)
-        shapes = {"q_proj": (spec.heads * spec.head_dim, spec.hidden), "k_proj": (spec.kv_heads * spec.head_dim, spec.hidden),
-                  "v_proj": (spec.kv_heads * spec.head_dim, spec.hidden), "o_proj": (spec.hidden, spec.heads * spec.head_dim),
-                  "gate_proj": (spec.ffn, spec.hidden), "up_proj": (spec.ffn, spec.hidden), "down_proj": (spec.hidden, spec.ffn)}
-        layers = []
-        for _ in range(spec.layers):
-            d = {}
-            for name, (N, K) in shapes.items():
-                m = AnyPrecisionLinear(K, N, bits, bias=False, device="meta")
-                m.qweight = packing.random_qweight(max(bits), N, K, device=dev, generator=gen)
-                for b in bits:
-                    setattr(m, f"lut{b}", packing.random_lut(N, b, device=dev, generator=gen))
-                d[name] = m
-            d["input_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
-            d["post_attention_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
-            layers.append(d)
-        embed = (torch.randn((spec.vocab, spec.hidden), device=dev, generator=gen) * 0.02).half()
-        head = (torch.randn((spec.vocab, spec.hidden), device=dev, generator=gen) * 0.02).half()
-        return cls(spec, layers, embed, torch.ones(spec.hidden, dtype=torch.float16, device=dev), head, dev, batch, max_seq)
+        heads, kv, ffn, D = spec.heads // tp_world, spec.kv_heads // tp_world, spec.ffn // tp_world, spec.head_dim
+        shapes = {"qkv_proj": ((heads + 2 * kv) * D, spec.hidden, gen), "o_proj": (spec.hidden, heads * D, common),
+                  "gate_up_proj": (2 * ffn, spec.hidden, gen), "down_proj": (spec.hidden, ffn, common)}
+
+        def layer_dicts():
+            for _ in range(spec.layers):
+                d = {}
+                for name, (N, K, lut_gen) in shapes.items():
+                    m = AnyPrecisionLinear(K, N, bits, bias=False, device="meta")
+                    m.qweight = packing.random_qweight(max(bits), N, K, device=dev, generator=gen)
+                    for b in bits:
+                        setattr(m, f"lut{b}", packing.random_lut(N, b, device=dev, generator=lut_gen))
+                    d[name] = m
+                d["qkv_proj"].split_sizes = [heads * D, kv * D, kv * D]
+                d["gate_up_proj"].split_sizes = [ffn, ffn]
+                d["input_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
+                d["post_attention_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
+                yield d
+
+        embed = (torch.randn((spec.vocab, spec.hidden), device=dev, generator=common) * 0.02).half()
+        head = (torch.randn((spec.vocab, spec.hidden), device=dev, generator=common) * 0.02).half()
+        return cls(spec, layer_dicts(), embed, torch.ones(spec.hidden, dtype=torch.float16, device=dev), head, dev, batch,
+                   max_seq, tp_world=tp_world, allreduce=allreduce, group=group)
 
     @classmethod
-    def from_packed(cls, path: str, device, precisions=None, batch: int = 1, max_seq: int = 1024):
+    def from_packed(cls, path: str, device, precisions=None, batch: int = 1, max_seq: int = 1024, tp_rank: int = 0,
+                    tp_world: int = 1, allreduce=None, group=None):
         """Build the model from a packed checkpoint directory written by the reference's packer (Llama
-        architecture: ``arch_config`` must name the seven Llama projections)."""
+        architecture: ``arch_config`` must name the seven Llama projections).  With ``tp_world`` > 1 every
+        rank reads the whole checkpoint and keeps its shard of every layer."""
         from . import checkpoint
         config, linears, rest = checkpoint.load_linears(path, precisions=precisions, device=None)
         arch = config["anyprec"]["arch_config"]
         spec = LlamaSpec.from_hf_config(config)
         prefix = f"{arch['model_name']}.{arch['layers_name']}"
-        layers = []
-        for L in range(spec.layers):
-            d = {}
-            for full in arch["module_names"]:
-                d[full.split(".")[-1]] = linears[f"{prefix}.{L}.{full}"]
-            missing = {"q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"} - set(d)
-            if missing:
-                raise ValueError(f"layer {L}: the checkpoint does not hold {sorted(missing)} (not a Llama-style model?)")
-            d["input_layernorm"] = rest[f"{prefix}.{L}.input_layernorm.weight"]
-            d["post_attention_layernorm"] = rest[f"{prefix}.{L}.post_attention_layernorm.weight"]
-            layers.append(d)
+        styles = {"q_proj": "col", "k_proj": "col", "v_proj": "col", "gate_proj": "col", "up_proj": "col",
+                  "o_proj": "row", "down_proj": "row"}
+
+        def layer_dicts():
+            for L in range(spec.layers):
+                d = {}
+                for full in arch["module_names"]:
+                    d[full.split(".")[-1]] = linears.pop(f"{prefix}.{L}.{full}")
+                missing = set(styles) - set(d)
+                if missing:
+                    raise ValueError(f"layer {L}: the checkpoint does not hold {sorted(missing)} (not a Llama-style model?)")
+                if tp_world > 1:
+                    d = {name: _shard_module(m.to(device), styles[name], tp_rank, tp_world) for name, m in d.items()}
+                d["input_layernorm"] = rest[f"{prefix}.{L}.input_layernorm.weight"]
+                d["post_attention_layernorm"] = rest[f"{prefix}.{L}.post_attention_layernorm.weight"]
+                yield d
+
         embed = rest[f"{arch['model_name']}.embed_tokens.weight"]
         head = rest.get("lm_head.weight", embed)
-        return cls(spec, layers, embed, rest[f"{arch['model_name']}.norm.weight"], head, device, batch, max_seq)
+        return cls(spec, layer_dicts(), embed, rest[f"{arch['model_name']}.norm.weight"], head, device, batch, max_seq,
+                   tp_world=tp_world, allreduce=allreduce, group=group)
+
+    def with_batch(self, batch: int, max_seq: int | None = None):
+        """A second model over the SAME weights (modules and tables are shared, nothing is copied) with KV
+        caches, buffers and decode graphs of its own for another batch size."""
+        other = object.__new__(type(self))
+        other.__dict__.update(self.__dict__)
+        other.batch, other.max_seq = batch, max_seq or self.max_seq
+        other.layers = []
+        for L in self.layers:
+            M = _Layer()
+            for name in ("qkv", "o", "gate_up", "down", "in_norm", "post_norm"):
+                setattr(M, name, getattr(L, name))
+            other.layers.append(M)
+        if other.max_seq != self.max_seq:
+            s = self.spec
+            inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float64) / s.head_dim))
+            ang = torch.arange(other.max_seq, dtype=torch.float64)[:, None] * inv[None, :]
+            other.cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).to(torch.float32).to(self.device).contiguous()
+        other._allocate_state()
+        return other
 
     # ------------------------------------------------------------------------------------ precision
     def set_precision(self, precision: int):
@@ -214,16 +299,25 @@ class AnyPrecisionLlama:
                                                  weight.data_ptr(), y.data_ptr(), rows, self.spec.hidden,
                                                  self.spec.rms_eps, self._stream()), "ap_add_rmsnorm")
 
-    def _layer_tail(self, L, h, y, attn):
+    def _reduce(self, t, decode: bool):
+        """Sum a row-parallel output over the ranks, in place."""
+        if self.tp_world > 1:
+            if decode and self.allreduce is not None:
+                self.allreduce(t)
+            else:
+                import torch.distributed as dist
+                dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def _layer_tail(self, L, h, y, attn, decode: bool):
         """o_proj, residual + norm, gate/up, SiLU * up, down; returns the MLP output (the caller adds it)."""
-        s = self.spec
-        o = L.o(attn)
+        o = self._reduce(L.o(attn), decode)
         self._add_rmsnorm(h, o, L.post_norm, y)
         gu = L.gate_up(y)
         rows = gu.shape[0]
-        act = self.act[:rows] if rows <= self.batch else torch.empty((rows, s.ffn), dtype=torch.float16, device=self.device)
-        _check(self.lib, self.lib.ap_silu_mul(gu.data_ptr(), act.data_ptr(), rows, s.ffn, self._stream()), "ap_silu_mul")
-        return L.down(act)
+        act = self.act[:rows] if rows <= self.batch else torch.empty((rows, self.ffn), dtype=torch.float16, device=self.device)
+        _check(self.lib, self.lib.ap_silu_mul(gu.data_ptr(), act.data_ptr(), rows, self.ffn, self._stream()), "ap_silu_mul")
+        return self._reduce(L.down(act), decode)
 
     # ------------------------------------------------------------------------------------ prefill
     @torch.inference_mode()
@@ -247,13 +341,13 @@ class AnyPrecisionLlama:
                 self._add_rmsnorm(h, mlp, L.in_norm, y)
                 qkv = L.qkv(y)                                             # [B*T, (H + 2 KV) * D]
                 _check(self.lib, self.lib.ap_rope_cache(qkv.data_ptr(), self.cos_sin.data_ptr(), pos.data_ptr(),
-                                                        L.k_cache.data_ptr(), L.v_cache.data_ptr(), B * T, T, s.heads,
-                                                        s.kv_heads, s.head_dim, self.max_seq, self._stream()), "ap_rope_cache")
-                q = qkv[:, :s.heads * s.head_dim].reshape(B, T, s.heads, s.head_dim).transpose(1, 2)   # [B, H, T, D]
+                                                        L.k_cache.data_ptr(), L.v_cache.data_ptr(), B * T, T, self.heads,
+                                                        self.kv_heads, s.head_dim, self.max_seq, self._stream()), "ap_rope_cache")
+                q = qkv[:, :self.heads * s.head_dim].reshape(B, T, self.heads, s.head_dim).transpose(1, 2)   # [B, H, T, D]
                 k, v = L.k_cache[:, :, :T], L.v_cache[:, :, :T]
-                attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=s.kv_heads != s.heads)
-                attn = attn.transpose(1, 2).reshape(B * T, s.heads * s.head_dim)
-                mlp = self._layer_tail(L, h, y, attn)
+                attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.kv_heads != self.heads)
+                attn = attn.transpose(1, 2).reshape(B * T, self.heads * s.head_dim)
+                mlp = self._layer_tail(L, h, y, attn, decode=False)
             self._add_rmsnorm(h, mlp, self.final_norm, y)
             last = y.view(B, T, s.hidden)[:, -1]
             self.pos.fill_(T)
@@ -270,15 +364,15 @@ class AnyPrecisionLlama:
             self._add_rmsnorm(self.h, mlp, L.in_norm, self.y)
             qkv = L.qkv(self.y)                                              # decode kernel: B <= 8 rows
             _check(self.lib, self.lib.ap_rope_cache(qkv.data_ptr(), self.cos_sin.data_ptr(), self.pos.data_ptr(),
-                                                    L.k_cache.data_ptr(), L.v_cache.data_ptr(), B, 1, s.heads, s.kv_heads,
+                                                    L.k_cache.data_ptr(), L.v_cache.data_ptr(), B, 1, self.heads, self.kv_heads,
                                                     s.head_dim, self.max_seq, self._stream()), "ap_rope_cache")
             _check(self.lib, self.lib.ap_decode_attention(qkv.data_ptr(), qkv.shape[1], L.k_cache.data_ptr(),
                                                           L.v_cache.data_ptr(), self.pos.data_ptr(), self.attn.data_ptr(), B,
-                                                          s.heads, s.kv_heads, s.head_dim, self.max_seq,
+                                                          self.heads, self.kv_heads, s.head_dim, self.max_seq,
                                                           1.0 / math.sqrt(s.head_dim), self.attn_splits,
                                                           self.attn_scratch.data_ptr() if self.attn_scratch is not None else None,
                                                           self._stream()), "ap_decode_attention")
-            mlp = self._layer_tail(L, self.h, self.y, self.attn)
+            mlp = self._layer_tail(L, self.h, self.y, self.attn, decode=True)
         self._add_rmsnorm(self.h, mlp, self.final_norm, self.y)
         logits = self.y @ self.lm_head.T
         self.tok.copy_(logits.argmax(dim=-1))

@@ -219,7 +219,10 @@ def run_ours(args):
 
     if world > 1:
         line = tensor_parallel_figures(args, rank, world, device, args.layers, full=True)
+        torch.cuda.empty_cache()
+        decoder70 = decoder_70b_figures(args, rank, world, device)
         if rank == 0:
+            line["decoder_llama2_70b"] = decoder70
             print(json.dumps(line))
         # A captured graph holds collective work; leave without the process-group destructor (it can block
         # on a communicator that graphs still use).  Only the benchmark process ends this way.
@@ -397,6 +400,7 @@ def run_ours(args):
     # The tensor-parallel workload (Llama-2-70B layer set) on this one GPU: the anchor of the 1/2/4/8 curve.
     tp1 = tensor_parallel_figures(args, 0, 1, device, args.layers, full=False)
     decoder = decoder_figures(args, device)
+    decoder70 = decoder_70b_figures(args, 0, 1, device)
     cpu = cpu_baseline_sample(kind_pref="port", seconds_hint=15)
 
     line = {
@@ -411,6 +415,7 @@ def run_ours(args):
         "prefill": prefill,
         "tp1_llama2_70b": tp1,
         "decoder_llama2_7b": decoder,
+        "decoder_llama2_70b": decoder70,
         "per_w_bits_gbs": per_w,
         "per_w_bits_frac_of_measured_peak": {k: round(v / peak, 3) for k, v in per_w.items()},
         "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
@@ -485,6 +490,76 @@ def decoder_figures(args, device):
     return {"model": "random-init Llama-2-7B decoder (32 layers, hidden 4096, 32 heads, FFN 11008, vocab 32000), every "
                      "linear an 8-bit-parent any-precision layer; q+k+v and gate+up stacked; one CUDA graph per precision",
             "prompt_tokens": prompt, "new_tokens": new, "batch": 1, "per_w_bits": out}
+
+
+def decoder_70b_figures(args, rank, world, device):
+    """Decode rate of a whole random-init Llama-2-70B decoder (80 layers, hidden 8192, 64 heads / 8 KV heads,
+    FFN 28672) tensor-parallel over `world` ranks: a 1024-token prompt of uniform random token ids, then greedy
+    decode steps at batch 1 and batch 8, w_bits 3, 4 and 8.  q/k/v/gate/up are split on their rows (heads, FFN
+    rows), o/down on their input columns with the one-shot all-reduce in the captured decode step and the process
+    group's all-reduce for the prompt.  Times are the max over ranks; `bound_tok_s` is what the measured HBM peak
+    allows for the bytes ONE rank must read per step (its planes and tables, the replicated fp16 lm_head)."""
+    import torch
+    import torch.distributed as dist
+
+    from anyprec_b200.decoder import AnyPrecisionLlama, LlamaSpec
+
+    spec = LlamaSpec.llama2_70b()
+    prompt, new = 1024, 33
+    allreduce = None
+    if world > 1:
+        from anyprec_b200.comm import OneShotAllReduce
+        allreduce = OneShotAllReduce(8 * spec.hidden * 2, device)
+    big = AnyPrecisionLlama.random_init(spec, device, supported_bits=(3, 4, 8), seed=4100, batch=8, max_seq=prompt + new,
+                                        tp_rank=rank, tp_world=world, allreduce=allreduce)
+    peak, _ = measured_peak_gbs()
+    local = [(m.out_features, m.in_features) for L in big.layers[:1] for m in (L.qkv, L.o, L.gate_up, L.down)]
+    out = {}
+    for batch in (1, 8):
+        model = big if batch == 8 else big.with_batch(1)
+        ids = torch.randint(0, spec.vocab, (batch, prompt), generator=torch.Generator().manual_seed(3))
+        for w in (3, 4, 8):
+            model.generate(ids, 3, precision=w)                               # captures this precision's decode graph
+            model.set_precision(w)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            logits = model.prefill(ids)
+            torch.cuda.synchronize()
+            prefill_ms = (time.perf_counter() - t0) * 1e3
+            model.tok.copy_(logits.argmax(-1))
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            with torch.cuda.stream(model._side):
+                g = model._graph(w)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(new - 1):
+                    g.replay()
+                b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / (new - 1), prefill_ms], device=device, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            step_ms = float(t[0])
+            step_bytes = spec.layers * sum(N * K * w // 8 + N * (1 << w) * 2 for N, K in local) + spec.vocab * spec.hidden * 2
+            bound = batch * peak * 1e9 / step_bytes
+            out[f"batch{batch}_w{w}"] = {"decode_tok_s": round(batch * 1e3 / step_ms, 1), "decode_ms_per_step": round(step_ms, 3),
+                                         "prefill_ms": round(float(t[1]), 1), "bound_tok_s": round(bound, 1),
+                                         "frac_of_bound": round(batch * 1e3 / step_ms / bound, 3)}
+    if allreduce is not None:
+        wait_expired = allreduce.wait_expired()
+        allreduce.close()
+    else:
+        wait_expired = False
+    del big, model
+    torch.cuda.empty_cache()
+    return {"model": "random-init Llama-2-70B decoder (80 layers, hidden 8192, 64 heads, 8 KV heads, FFN 28672, vocab 32000), "
+                     "every linear an 8-bit-parent any-precision layer",
+            "parallelism": f"tp{world}", "prompt_tokens": prompt, "decode_steps_timed": new - 1,
+            "allreduce_wait_expired": bool(wait_expired), "cases": out}
 
 # ----------------------------------------------------------------------------- tensor-parallel workload
 def tensor_parallel_figures(args, rank, world, device, layers, full):
