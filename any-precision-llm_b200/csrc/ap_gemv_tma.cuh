@@ -358,7 +358,12 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
 #pragma unroll
                         for (int j = 0; j < 4; j++) xv[j] = make_uint4(0u, 0u, 0u, 0u);
                     }
+#ifdef AP_GEMV_LAB_NO_WORD_MATH
+                    // lab builds only: everything but the per-word arithmetic (loads, waits, hand-back, reduction)
+                    acc[0][0] += __uint_as_float((wa[0] ^ wb[W - 1] ^ xv[0].x ^ xv[3].w) & 0x3fffffffu);
+#else
                     process_word<W, T::kMode>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, table_const, valid_w);
+#endif
                 }
             };
             if (8 * sl + 8 <= cw_words) two_words(TrueType{});
