@@ -66,6 +66,10 @@ def load_library() -> ctypes.CDLL:
     lib.ap_matmul_kbit_workspace_bytes.argtypes = [i, i, i]
     lib.ap_matmul_kbit_splitk.restype = i
     lib.ap_matmul_kbit_splitk.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, vp]
+    lib.ap_matmul_kbit_gated.restype = i
+    lib.ap_matmul_kbit_gated.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, vp]
+    lib.ap_silu_mul.restype = i
+    lib.ap_silu_mul.argtypes = [vp, vp, i, i, i, vp]
     lib.ap_gemm_kbit.restype = i
     lib.ap_gemm_kbit.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, vp, vp]
     lib.ap_gemm_kbit_splits.restype = i
@@ -251,12 +255,15 @@ def reserve_workspace(device=None, nbytes: int = _MIN_WORKSPACE) -> int:
 
 
 def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bits: int, *,
-                out: torch.Tensor | None = None, splits: int | None = None):
+                out: torch.Tensor | None = None, splits: int | None = None, gated: bool = False):
     """``x @ W_w.T`` for fp16 ``x[..., K]``; returns fp16 ``[..., N]``.
 
     Same call as the reference's ``matmul_kbit`` (kernels/main.cu:93-143).  ``splits`` (default:
     chosen from the shape) cuts K into ranges taken by different thread blocks, for layers with too
     few rows to fill the GPU; the scratch it needs is kept per device and stream by this module.
+    ``gated=True`` (no counterpart in the reference): the operand holds a gated MLP's gate and up
+    projections stacked tile by tile (``packing.interleave_gate_up``) and the result is
+    ``silu(gate) * up`` of shape ``[..., N / 2]``; at most eight rows, fast-kernel shapes only.
     """
     N, K, plane_stride = _check_operands(qweight, lut, w_bits)
     if x.dtype != torch.float16:
@@ -275,9 +282,12 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
     if M == 0:
         return torch.empty((*lead, N), dtype=torch.float16, device=x.device)
     lib = load_library()
+    n_out = N // 2 if gated else N
+    if gated and (N % 16 or M > 8):
+        raise ValueError("gated=True needs a row count that is a multiple of 16 and at most eight activation rows")
     if out is None:
-        out = torch.empty((*lead, N), dtype=torch.float16, device=x.device)
-    elif tuple(out.shape) != (*lead, N) or out.dtype != torch.float16 or not out.is_contiguous() \
+        out = torch.empty((*lead, n_out), dtype=torch.float16, device=x.device)
+    elif tuple(out.shape) != (*lead, n_out) or out.dtype != torch.float16 or not out.is_contiguous() \
             or out.device != x.device:
         raise ValueError("out must be a contiguous float16 [..., N] tensor on the operands' device")
     with _on_device(x.device):
@@ -285,7 +295,11 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
         if splits is None:
             splits = _pick_splits(x.device, N, K)
         ws = _workspace(lib, x.device, stream, M, N, splits) if splits > 1 else None
-        if ws is None:
+        if gated:
+            rc = lib.ap_matmul_kbit_gated(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),
+                                          M, N, K, w_bits, splits if ws is not None else 1,
+                                          ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
+        elif ws is None:
             rc = lib.ap_matmul_kbit(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),
                                     M, N, K, w_bits, stream)
         else:
@@ -293,6 +307,36 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
                                            out.data_ptr(), M, N, K, w_bits, splits, ws.data_ptr(), ws.numel(), stream)
     if rc != 0:
         _raise(lib, rc, "matmul_kbit")
+    return out
+
+
+def gated_supported(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor) -> bool:
+    """Whether ``matmul_kbit(..., gated=True)`` takes these operands: up to eight rows, ``K % 128 == 0``,
+    ``N % 16 == 0``, 16-byte aligned ``x``, ``qweight`` and ``lut``, the TMA loader not switched off."""
+    rows = x.numel() // x.shape[-1]
+    K = qweight.shape[2] * 32
+    return (rows <= 8 and K % 128 == 0 and qweight.shape[1] % 16 == 0 and qweight.stride(0) % 4 == 0 and
+            (x.data_ptr() | qweight.data_ptr() | lut.data_ptr()) % 16 == 0 and
+            not os.environ.get("AP_GEMV_LOADER", "").startswith("c"))
+
+
+def silu_mul(gate_up: torch.Tensor, *, tiled: bool = False, out: torch.Tensor | None = None):
+    """``silu(gate) * up`` for fp16 ``gate_up[..., 2 F]`` holding ``gate | up`` side by side or
+    (``tiled``) tile by tile as ``matmul_kbit`` returns them for a ``packing.interleave_gate_up`` operand.
+    No counterpart in the reference (it leaves this to the framework's MLP)."""
+    if gate_up.dtype != torch.float16 or not gate_up.is_cuda or not gate_up.is_contiguous() or gate_up.shape[-1] % 2:
+        raise ValueError("gate_up must be a contiguous float16 CUDA tensor with an even last dimension")
+    F = gate_up.shape[-1] // 2
+    rows = gate_up.numel() // (2 * F)
+    if out is None:
+        out = torch.empty((*gate_up.shape[:-1], F), dtype=torch.float16, device=gate_up.device)
+    elif out.numel() != rows * F or out.dtype != torch.float16 or not out.is_contiguous() or out.device != gate_up.device:
+        raise ValueError("out must be a contiguous float16 [..., F] tensor on the operand's device")
+    lib = load_library()
+    with _on_device(gate_up.device):
+        rc = lib.ap_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, F, 1 if tiled else 0, _current_stream(gate_up.device))
+    if rc != 0:
+        _raise(lib, rc, "silu_mul")
     return out
 
 

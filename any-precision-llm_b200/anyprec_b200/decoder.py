@@ -9,9 +9,11 @@ and its ``fuse_layers`` is a stub (:186-190).  This class keeps that calling con
 reference leaves open:
 
 * q, k and v are one ``AnyPrecisionLinear`` (rows stacked, ``AnyPrecisionLinear.fuse``), gate and up
-  likewise, so a decoder layer issues four any-precision launches;
-* residual add + RMSNorm, rotary embedding + KV-cache write and SiLU * up are one small kernel each
-  (``ap_add_rmsnorm``, ``ap_rope_cache``, ``ap_silu_mul``);
+  another (rows stacked tile by tile, ``AnyPrecisionLinear.fuse_gated``), so a decoder layer issues four
+  any-precision launches;
+* residual add + RMSNorm and rotary embedding + KV-cache write are one small kernel each
+  (``ap_add_rmsnorm``, ``ap_rope_cache``); SiLU * up is the epilogue of the gate+up launch in a decode
+  step (``ap_matmul_kbit_gated``) and one small kernel (``ap_silu_mul``) after the prompt's GEMM;
 * a decode step reads its position from device memory, so one CUDA graph per precision is captured
   once and replayed for every generated token.
 
@@ -78,8 +80,6 @@ def _ops():
     lib.ap_add_rmsnorm.argtypes = [vp, vp, vp, vp, i, i, f, vp]
     lib.ap_rope_cache.restype = i
     lib.ap_rope_cache.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, vp]
-    lib.ap_silu_mul.restype = i
-    lib.ap_silu_mul.argtypes = [vp, vp, i, i, vp]
     lib.ap_decode_attention.restype = i
     lib.ap_decode_attention.argtypes = [vp, i, vp, vp, vp, vp, i, i, i, i, i, f, i, vp, vp]
     lib.ap_decode_attention_scratch_bytes.restype = ctypes.c_size_t
@@ -151,7 +151,9 @@ class AnyPrecisionLlama:
                 AnyPrecisionLinear.fuse([src["q_proj"].to(dev), src["k_proj"].to(dev), src["v_proj"].to(dev)])
             L.o = src["o_proj"].to(dev)
             L.gate_up = src["gate_up_proj"].to(dev) if "gate_up_proj" in src else \
-                AnyPrecisionLinear.fuse([src["gate_proj"].to(dev), src["up_proj"].to(dev)])
+                AnyPrecisionLinear.fuse_gated(src["gate_proj"].to(dev), src["up_proj"].to(dev))
+            if not getattr(L.gate_up, "gated", False):
+                raise ValueError("gate_up_proj must come from AnyPrecisionLinear.fuse_gated (rows stacked tile by tile)")
             L.down = src["down_proj"].to(dev)
             if L.qkv.out_features != (self.heads + 2 * self.kv_heads) * s.head_dim or L.down.in_features != self.ffn:
                 raise ValueError("layer shapes do not match the model dimensions (and tp_world)")
@@ -217,7 +219,7 @@ class AnyPrecisionLlama:
                         setattr(m, f"lut{b}", packing.random_lut(N, b, device=dev, generator=lut_gen))
                     d[name] = m
                 d["qkv_proj"].split_sizes = [heads * D, kv * D, kv * D]
-                d["gate_up_proj"].split_sizes = [ffn, ffn]
+                d["gate_up_proj"].gated = True              # random rows: any stacking order is as good as another
                 d["input_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
                 d["post_attention_layernorm"] = torch.ones(spec.hidden, dtype=torch.float16, device=dev)
                 yield d
@@ -313,10 +315,9 @@ class AnyPrecisionLlama:
         """o_proj, residual + norm, gate/up, SiLU * up, down; returns the MLP output (the caller adds it)."""
         o = self._reduce(L.o(attn), decode)
         self._add_rmsnorm(h, o, L.post_norm, y)
-        gu = L.gate_up(y)
-        rows = gu.shape[0]
+        rows = y.shape[0]
         act = self.act[:rows] if rows <= self.batch else torch.empty((rows, self.ffn), dtype=torch.float16, device=self.device)
-        _check(self.lib, self.lib.ap_silu_mul(gu.data_ptr(), act.data_ptr(), rows, self.ffn, self._stream()), "ap_silu_mul")
+        L.gate_up.forward_gated(y, out=act)
         return self._reduce(L.down(act), decode)
 
     # ------------------------------------------------------------------------------------ prefill

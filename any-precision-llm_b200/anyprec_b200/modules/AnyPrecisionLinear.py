@@ -144,6 +144,49 @@ class AnyPrecisionLinear(nn.Module):
         fused.split_sizes = [l.out_features for l in layers]
         return fused
 
+    @classmethod
+    def fuse_gated(cls, gate, up):
+        """One module for the gate and up projections of a gated MLP, rows stacked tile by tile (of every 16
+        rows eight gate rows, then the up rows of the same features: ``packing.interleave_gate_up``), so that
+        a decode step gets ``silu(gate) * up`` out of one launch (``forward_gated``).  ``forward`` of the
+        result returns the tiled order.  No counterpart in the reference."""
+        from .. import packing
+        if (gate.in_features, gate.out_features, gate.supported_bits, gate.precisions) != \
+                (up.in_features, up.out_features, up.supported_bits, up.precisions) or gate.bias is not None or \
+                up.bias is not None:
+            raise RuntimeError('gate and up must agree in shape, supported_bits and precisions and have no bias')
+        fused = cls(gate.in_features, 2 * gate.out_features, list(gate.supported_bits), bias=False,
+                    precisions=list(gate.precisions), device='meta')
+        q, luts = packing.interleave_gate_up(
+            gate.qweight, up.qweight, {b: getattr(gate, f'lut{b}') for b in gate.supported_bits if hasattr(gate, f'lut{b}')},
+            {b: getattr(up, f'lut{b}') for b in up.supported_bits if hasattr(up, f'lut{b}')})
+        fused.qweight = q
+        for b in gate.supported_bits:
+            if b in luts:
+                setattr(fused, f'lut{b}', luts[b])
+            elif hasattr(fused, f'lut{b}'):
+                delattr(fused, f'lut{b}')
+        fused.precision = gate.precision
+        fused.gated = True
+        return fused
+
+    def forward_gated(self, x, out=None, **kwargs):
+        """``silu(gate(x)) * up(x)`` of a ``fuse_gated`` module, ``[..., out_features / 2]``: one launch with the
+        activation in the kernel's epilogue for up to eight rows of shapes the decode kernel takes, the plain
+        product followed by ``ap_silu_mul`` otherwise.  Both round alike (each projection to fp16, the
+        activation to fp16, then the product)."""
+        if not getattr(self, 'gated', False):
+            raise RuntimeError('forward_gated needs a module built by fuse_gated')
+        w_bits = kwargs['precision'] if 'precision' in kwargs else self.precision
+        lut = self._buffers.get(f'lut{w_bits}')
+        if lut is None:
+            raise RuntimeError(f'{w_bits}-bit table is not loaded; available: {self.precisions}')
+        rows = x.numel() // x.shape[-1]
+        if _ext.gated_supported(x, self.qweight, lut):
+            return _ext.matmul_kbit(x, self.qweight, lut, w_bits, gated=True, out=out)
+        gu = self.forward(x, **kwargs)
+        return _ext.silu_mul(gu, tiled=True, out=out)
+
     def forward_split(self, x, **kwargs):
         """``forward`` of a fused module, cut back into the original layers' outputs (views)."""
         return torch.split(self.forward(x, **kwargs), getattr(self, 'split_sizes', [self.out_features]), dim=-1)

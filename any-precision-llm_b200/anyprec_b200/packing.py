@@ -153,6 +153,23 @@ def concat_rows(qweights, luts):
     return q, {w: torch.cat([l[w] for l in luts], dim=0).contiguous() for w in sorted(common)}
 
 
+def interleave_gate_up(gate_q: torch.Tensor, up_q: torch.Tensor, gate_luts: dict, up_luts: dict):
+    """The operand of ``matmul_kbit(..., gated=True)``: the two projections of a gated MLP stacked tile by
+    tile, of every 16 rows the first eight the gate rows ``f .. f+7`` and the last eight the up rows of the
+    same features.  Rows carry their own planes and tables, so nothing is re-packed.  Feature count a
+    multiple of 8."""
+    planes, F, words = gate_q.shape
+    if up_q.shape != gate_q.shape or F % 8:
+        raise ValueError("gate and up must have the same shape and a row count that is a multiple of 8")
+    q = torch.stack([gate_q.reshape(planes, F // 8, 8, words), up_q.reshape(planes, F // 8, 8, words)], dim=2)
+    q = q.reshape(planes, 2 * F, words).contiguous()
+    luts = {}
+    for b in sorted(set(gate_luts) & set(up_luts)):
+        g, u = gate_luts[b], up_luts[b]
+        luts[b] = torch.stack([g.reshape(F // 8, 8, -1), u.reshape(F // 8, 8, -1)], dim=1).reshape(2 * F, -1).contiguous()
+    return q, luts
+
+
 def random_qweight(planes: int, N: int, K: int, *, device, generator=None) -> torch.Tensor:
     """Bitplanes of i.i.d. uniform parent codes: every bit is a fair coin, so the planes can
     be drawn directly without packing."""

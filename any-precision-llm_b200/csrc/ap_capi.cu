@@ -73,7 +73,7 @@ size_t ticket_bytes(int) { return kTicketAreaBytes; }
 bool tickets_fit(int N) { return static_cast<size_t>((N + 15) / 16) * sizeof(int) <= kTicketAreaBytes; }
 
 int matmul_impl(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out, int M, int N,
-                int K, int w_bits, int splits, void* workspace, size_t workspace_bytes, void* stream) {
+                int K, int w_bits, int splits, void* workspace, size_t workspace_bytes, void* stream, int gated = 0) {
     int rc = check_common(qweight, plane_stride, lut, out, N, K, w_bits);
     if (rc != AP_OK) return rc;
     if (!x) return AP_ERR_NULL_POINTER;
@@ -94,7 +94,8 @@ int matmul_impl(const void* x, const void* qweight, int64_t plane_stride, const 
     char* op = static_cast<char*>(out);
     // eight batch rows per pass over the planes; the launcher runs the passes (side by side where it can)
     cudaError_t e = ap::launch_gemv(xp, qweight, plane_stride, lut, op, M, N, K, w_bits, splits, partials, tickets,
-                                    static_cast<cudaStream_t>(stream));
+                                    static_cast<cudaStream_t>(stream), gated);
+    if (e == cudaErrorNotSupported) return AP_ERR_UNSUPPORTED;
     return e == cudaSuccess ? AP_OK : cuda_fail(e);
 }
 
@@ -115,6 +116,13 @@ extern "C" int ap_matmul_kbit_splitk(const void* x, const void* qweight, int64_t
                                      size_t workspace_bytes, void* stream) {
     if (splits < 1) return AP_ERR_BAD_SHAPE;
     return matmul_impl(x, qweight, plane_stride, lut, out, M, N, K, w_bits, splits, workspace, workspace_bytes, stream);
+}
+
+extern "C" int ap_matmul_kbit_gated(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out,
+                                    int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+    if (splits < 1 || N % 16 != 0 || M > 8) return M > 8 || N % 16 ? AP_ERR_UNSUPPORTED : AP_ERR_BAD_SHAPE;
+    return matmul_impl(x, qweight, plane_stride, lut, out, M, N, K, w_bits, splits, workspace, workspace_bytes, stream, 1);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -10,7 +10,7 @@
 //   ap_add_rmsnorm   h += delta (optional), y = h * rsqrt(mean(h^2) + eps) * weight      one block per row
 //   ap_rope_cache    rotary embedding of q and k at each row's position, k and v written into the
 //                    KV cache at that position                                           one block per row
-//   ap_silu_mul      y = silu(gate) * up for gate|up stored side by side                 grid-stride
+//   ap_silu_mul      y = silu(gate) * up for gate|up side by side or tile by tile         grid-stride
 //   ap_decode_attention  one query per sequence against its KV cache up to the query's position
 //                    (grouped-query heads), softmax in fp32                              one block per (head, sequence)
 // All fp16 in and out with fp32 arithmetic.  Positions come from device memory, so that a captured
@@ -127,14 +127,16 @@ rope_cache_kernel(__half* __restrict__ qkv, const float* __restrict__ cos_sin, c
 }
 
 __global__ void __launch_bounds__(256)
-silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ y, int rows, int ffn) {
+silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ y, int rows, int ffn, int tiled) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t total = (size_t)rows * ffn / 2;
     for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it < total; it += (size_t)gridDim.x * blockDim.x) {
         const size_t row = (it * 2) / ffn, i = (it * 2) % ffn;
-        const float2 g = __half22float2(*reinterpret_cast<const __half2*>(gate_up + row * 2 * ffn + i));
-        const float2 u = __half22float2(*reinterpret_cast<const __half2*>(gate_up + row * 2 * ffn + ffn + i));
+        // gate | up side by side, or (tiled) eight gate then eight up values of the same features in every 16
+        const size_t gi = tiled ? (i >> 3) * 16 + (i & 7) : i, ui = tiled ? gi + 8 : ffn + i;
+        const float2 g = __half22float2(*reinterpret_cast<const __half2*>(gate_up + row * 2 * ffn + gi));
+        const float2 u = __half22float2(*reinterpret_cast<const __half2*>(gate_up + row * 2 * ffn + ui));
         // silu in fp32, rounded to fp16 before the product, as a framework would evaluate act(gate) * up
         const __half2 a = __floats2half2_rn(g.x / (1.f + __expf(-g.x)), g.y / (1.f + __expf(-g.y)));
         const float2 af = __half22float2(a);
@@ -340,15 +342,15 @@ extern "C" int ap_rope_cache(void* qkv, const void* cos_sin, const void* pos, vo
     return e == cudaSuccess ? AP_OK : AP_ERR_LAUNCH;
 }
 
-extern "C" int ap_silu_mul(const void* gate_up, void* y, int rows, int ffn, void* stream) {
+extern "C" int ap_silu_mul(const void* gate_up, void* y, int rows, int ffn, int tiled, void* stream) {
     if (!gate_up || !y) return AP_ERR_NULL_POINTER;
-    if (rows < 1 || ffn < 2 || ffn % 2) return AP_ERR_BAD_SHAPE;
+    if (rows < 1 || ffn < 2 || ffn % 2 || (tiled && ffn % 8)) return AP_ERR_BAD_SHAPE;
     if ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(y)) & 3) return AP_ERR_BAD_ALIGNMENT;
     const size_t total = (size_t)rows * ffn / 2;
     int blocks = (int)((total + 255) / 256);
     if (blocks > 1184) blocks = 1184;
     cudaError_t e = launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), static_cast<cudaStream_t>(stream),
-                               static_cast<const __half*>(gate_up), static_cast<__half*>(y), rows, ffn);
+                               static_cast<const __half*>(gate_up), static_cast<__half*>(y), rows, ffn, tiled);
     return e == cudaSuccess ? AP_OK : AP_ERR_LAUNCH;
 }
 

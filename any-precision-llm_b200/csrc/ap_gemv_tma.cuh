@@ -101,7 +101,7 @@ __device__ __forceinline__ void tensor_g2s_3d(uint32_t dst, const CUtensorMap* m
         : "memory");
 }
 
-template <int W, int OCC, int MODE>
+template <int W, int OCC, int MODE, bool GATED = false>
 __global__ void __launch_bounds__(kGemvMaxWarps * 32, OCC)
 gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __restrict__ x,
                      const uint16_t* __restrict__ lut, __half* __restrict__ out, int M, int N, int K, int mpad,
@@ -396,13 +396,32 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     mine[(g + 8) * 8 + 2 * t] = acc[0][2] + acc[1][2];
     mine[(g + 8) * 8 + 2 * t + 1] = acc[0][3] + acc[1][3];
     __syncthreads();
+    // GATED: the 16 rows of a tile are eight gate rows followed by the eight up rows of the same
+    // features (a gated MLP's two projections stacked tile by tile), and the tile's output is the eight
+    // values silu(gate) * up, rounded like the separate operations would be (both projections to fp16,
+    // the activation to fp16, then the product).
+    auto gate = [](float gsum, float usum) {
+        const float gf = __half2float(__float2half_rn(gsum)), uf = __half2float(__float2half_rn(usum));
+        const float a = __half2float(__float2half_rn(gf / (1.f + __expf(-gf))));
+        return __float2half_rn(a * uf);
+    };
     if (gridDim.y == 1) {
-        for (int i = tid; i < 16 * M; i += kThreads) {
-            const int m = i >> 4, r = i & 15;            // 16 consecutive rows per m: 32-byte stores
-            float sum = 0.f;
+        if constexpr (!GATED) {
+            for (int i = tid; i < 16 * M; i += kThreads) {
+                const int m = i >> 4, r = i & 15;            // 16 consecutive rows per m: 32-byte stores
+                float sum = 0.f;
 #pragma unroll
-            for (int w2 = 0; w2 < kGemvMaxWarps; w2++) sum += red[w2 * 128 + r * 8 + m];
-            out[(size_t)m * N + row0 + r] = __float2half_rn(sum);
+                for (int w2 = 0; w2 < kGemvMaxWarps; w2++) sum += red[w2 * 128 + r * 8 + m];
+                out[(size_t)m * N + row0 + r] = __float2half_rn(sum);
+            }
+        } else {
+            for (int i = tid; i < 8 * M; i += kThreads) {
+                const int m = i >> 3, r = i & 7;
+                float gs = 0.f, us = 0.f;
+#pragma unroll
+                for (int w2 = 0; w2 < kGemvMaxWarps; w2++) { gs += red[w2 * 128 + r * 8 + m]; us += red[w2 * 128 + (r + 8) * 8 + m]; }
+                out[(size_t)m * (N >> 1) + (row0 >> 1) + r] = gate(gs, us);
+            }
         }
     } else {
         // Split-K: park this split's fp32 tile in the workspace; the CTA that draws the last ticket
@@ -422,11 +441,23 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
         __syncthreads();
         if (*flag) {
             __threadfence();
-            for (int i = tid; i < 16 * M; i += kThreads) {
-                const int m = i >> 4, r = i & 15;
-                float sum = 0.f;
-                for (int sp = 0; sp < S; sp++) sum += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r);
-                out[(size_t)m * N + row0 + r] = __float2half_rn(sum);
+            if constexpr (!GATED) {
+                for (int i = tid; i < 16 * M; i += kThreads) {
+                    const int m = i >> 4, r = i & 15;
+                    float sum = 0.f;
+                    for (int sp = 0; sp < S; sp++) sum += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r);
+                    out[(size_t)m * N + row0 + r] = __float2half_rn(sum);
+                }
+            } else {
+                for (int i = tid; i < 8 * M; i += kThreads) {
+                    const int m = i >> 3, r = i & 7;
+                    float gs = 0.f, us = 0.f;
+                    for (int sp = 0; sp < S; sp++) {
+                        gs += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r);
+                        us += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r + 8);
+                    }
+                    out[(size_t)m * (N >> 1) + (row0 >> 1) + r] = gate(gs, us);
+                }
             }
             if (tid == 0) tickets[blockIdx.x] = 0;
         }
@@ -476,7 +507,7 @@ static bool encode_plane_map(CUtensorMap* map, const void* qweight, long long pl
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int W, int OCC, int MODE>
+template <int W, int OCC, int MODE, bool GATED = false>
 static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const uint16_t* lut, __half* out, int M, int N,
                                   int K, int splits, int split_chunks, float* partials, int* tickets, cudaStream_t stream) {
     using T = GemvTmaCfg<W, OCC, MODE>;
@@ -487,7 +518,7 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         int most = 0;
         for (int mp = 1; mp <= 8; mp *= 2) most = T::total(mp) > most ? T::total(mp) : most;
-        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
@@ -502,15 +533,16 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE>, map, x, lut, out, M, N, K, mpad, split_chunks, partials,
-                              tickets);
+    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, GATED>, map, x, lut, out, M, N, K, mpad, split_chunks,
+                              partials, tickets);
 }
 
 template <int W>
 static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plane_stride, const uint16_t* lut, __half* out,
                               int M, int N, int K, int splits, float* partials, int* tickets, cudaStream_t stream,
-                              bool* used) {
+                              bool* used, int gated = 0) {
     *used = false;
+    if (gated && M > 8) return cudaSuccess;                  // the gated epilogue is for decode batches
     CUtensorMap map;
     if (!make_plane_map(&map, q, plane_stride, N, K, W)) return cudaSuccess;      // caller falls back to cp.async
     const int chunks = (K + 1023) / 1024;
@@ -530,7 +562,8 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
     if (M > 8 && splits > 1) { *used = false; return cudaSuccess; }              // the caller runs the passes one by one
     const bool many_blocks = (long long)(N / 16) * splits * ((M + 7) / 8) >= 3LL * sms;
 #define AP_TMA_GO(OCC_, MODE_) \
-    return launch_tma_occ<W, OCC_, MODE_>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream)
+    return gated ? launch_tma_occ<W, OCC_, MODE_, true>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream) \
+                 : launch_tma_occ<W, OCC_, MODE_, false>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream)
     if constexpr (W == 3) {
         if (many_blocks) AP_TMA_GO(3, 2);
         AP_TMA_GO(2, 2);

@@ -13,9 +13,12 @@ cudaError_t launch_dequant(const void* qweight, long long plane_stride, const vo
 // `splits` > 1 cuts K into that many ranges handled by different CTAs (fast kernel only); it needs
 // `partials` (splits*M*N floats, any contents) and `tickets` (N/16 ints, zero on entry, zero again
 // on completion).  With splits <= 1 or null scratch pointers every CTA takes a whole row range.
+// `gated` != 0: the rows are a gated MLP's gate and up projections stacked tile by tile (eight gate rows, then
+// the eight up rows of the same features, per 16 rows) and `out` is [M][N/2] = silu(gate) * up; only the fast
+// kernel has that epilogue (cudaErrorNotSupported otherwise; M <= 8).
 cudaError_t launch_gemv(const void* x, const void* qweight, long long plane_stride, const void* lut, void* out,
                         int M, int N, int K, int w_bits, int splits, float* partials, int* tickets,
-                        cudaStream_t stream);
+                        cudaStream_t stream, int gated = 0);
 bool gemv_fast_path(const void* x, const void* qweight, long long plane_stride, const void* lut, int N, int K);
 // Reads (after synchronising the device) and clears the flag that a decode kernel sets when one of its
 // bounded waits ran out.

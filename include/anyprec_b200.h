@@ -100,6 +100,20 @@ int ap_matmul_kbit_splitk(const void* x, const void* qweight, int64_t plane_stri
                           void* stream);
 
 /*
+ * matmul_kbit of a gated MLP's two projections at once, with the activation in the epilogue.  No counterpart
+ * in the reference (it calls gate_proj and up_proj separately and leaves act(gate) * up to the framework).
+ * qweight / lut hold BOTH projections stacked tile by tile: of every 16 rows the first eight are gate rows
+ * f .. f+7 and the last eight the up rows of the same features (N = 2 * features, a multiple of 16;
+ * packing.interleave_gate_up builds that operand).  out[M][N/2] (fp16) = silu(gate) * up, rounded as the
+ * separate operations would round (both products to fp16, the activation to fp16, then their product).
+ * M <= 8 and operands that the fast kernel takes (K % 128 == 0, 16-byte aligned x, qweight, lut) only:
+ * AP_ERR_UNSUPPORTED otherwise.  `splits`, `workspace` as for ap_matmul_kbit_splitk (splits = 1: no workspace).
+ */
+int ap_matmul_kbit_gated(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out,
+                         int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/*
  * ap_matmul_kbit_splitk for callers that have no way to provide a workspace: code that runs where
  * device allocation is off limits (inside a serving loop with a frozen memory pool, under a
  * framework that owns every byte of device memory, in a plugin that is handed only its inputs and
@@ -212,7 +226,9 @@ int ap_unpack_codes(const void* qweight, int64_t plane_stride, void* codes, int 
  *                   [sequences][kv_heads][max_seq][head_dim] (rows_per_seq = 1 for a decode step).
  *                   cos_sin: fp32 [max_seq][head_dim] = cos(head_dim/2) | sin(head_dim/2) per position;
  *                   pos: device int32[rows] (a row whose position is outside [0, max_seq) is skipped)
- *   ap_silu_mul     y[rows][ffn] = silu(gate) * up for gate_up[rows][2 * ffn] = gate | up
+ *   ap_silu_mul     y[rows][ffn] = silu(gate) * up for gate_up[rows][2 * ffn] = gate | up, or (tiled != 0,
+ *                   ffn % 8 == 0) of every 16 values eight gate then eight up values of the same features:
+ *                   the output of a plain product with the operand of ap_matmul_kbit_gated
  *   ap_decode_attention  one query token per sequence: out[b][h][:] = softmax(q . K[0..pos[b]] * scale) V[0..pos[b]]
  *                   with q = qkv[b * q_row_stride + h * head_dim ...] (the rotated q part of the q|k|v row),
  *                   caches as in ap_rope_cache, grouped-query heads (heads % kv_heads == 0), head_dim 32, 64,
@@ -226,7 +242,7 @@ int ap_add_rmsnorm(void* h, const void* delta, const void* weight, void* y, int 
                    void* stream);
 int ap_rope_cache(void* qkv, const void* cos_sin, const void* pos, void* k_cache, void* v_cache, int rows,
                   int rows_per_seq, int heads, int kv_heads, int head_dim, int max_seq, void* stream);
-int ap_silu_mul(const void* gate_up, void* y, int rows, int ffn, void* stream);
+int ap_silu_mul(const void* gate_up, void* y, int rows, int ffn, int tiled, void* stream);
 size_t ap_decode_attention_scratch_bytes(int sequences, int heads, int head_dim, int splits);
 int ap_decode_attention(const void* qkv, int q_row_stride, const void* k_cache, const void* v_cache, const void* pos,
                         void* out, int sequences, int heads, int kv_heads, int head_dim, int max_seq, float scale,

@@ -126,3 +126,20 @@ def test_module_chooses_the_prefill_path_by_the_measured_rule():
     assert mid._use_fused(x, 64, 3) and not mid._use_fused(x, 65, 3) and mid._route(x, 12, 3) == "fused"
     odd = AnyPrecisionLinear(1024 + 128, 100 * 128, [3], bias=False, device="cpu")   # in_features % 256 != 0
     assert not odd._use_fused(torch.zeros((64, 1152), dtype=torch.float16), 64, 3)
+
+
+def test_interleave_gate_up_layout():
+    from anyprec_b200 import packing
+    F, words = 24, 4
+    g = torch.arange(3 * F * words, dtype=torch.int32).reshape(3, F, words)
+    u = -g - 1
+    gl = {3: torch.arange(F * 8, dtype=torch.float16).reshape(F, 8)}
+    ul = {3: -gl[3] - 1}
+    q, luts = packing.interleave_gate_up(g, u, gl, ul)
+    assert q.shape == (3, 2 * F, words) and luts[3].shape == (2 * F, 8)
+    for f in range(F):
+        row = (f // 8) * 16 + f % 8
+        assert torch.equal(q[:, row], g[:, f]) and torch.equal(q[:, row + 8], u[:, f])
+        assert torch.equal(luts[3][row], gl[3][f]) and torch.equal(luts[3][row + 8], ul[3][f])
+    with pytest.raises(ValueError):
+        packing.interleave_gate_up(g[:, :20], u[:, :20], gl, ul)
