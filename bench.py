@@ -401,6 +401,7 @@ def run_ours(args):
     tp1 = tensor_parallel_figures(args, 0, 1, device, args.layers, full=False)
     decoder = decoder_figures(args, device)
     decoder70 = decoder_70b_figures(args, 0, 1, device)
+    quantizer = quantizer_figures(device)
     cpu = cpu_baseline_sample(kind_pref="port", seconds_hint=15)
 
     line = {
@@ -416,6 +417,7 @@ def run_ours(args):
         "tp1_llama2_70b": tp1,
         "decoder_llama2_7b": decoder,
         "decoder_llama2_70b": decoder70,
+        "quantizer": quantizer,
         "per_w_bits_gbs": per_w,
         "per_w_bits_frac_of_measured_peak": {k: round(v / peak, 3) for k, v in per_w.items()},
         "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
@@ -438,6 +440,43 @@ def run_ours(args):
     return line
 
 
+
+
+# ------------------------------------------------------------------------------------- quantiser
+def quantizer_figures(device):
+    """Seed (3-bit) + upscale (to 8-bit) quantisation of the three Llama-2-7B layer shapes on the GPU
+    (`ap_seed_upscale`, one thread block per row), in rows and weights per second, with the CPU checker's
+    row routine timed on a few rows of the same data beside it (one core, plain Python + numpy)."""
+    import numpy as np
+    import torch
+
+    from anyprec_b200 import quantize
+    from oracle import seed_upscale as su
+
+    out = {}
+    gen = torch.Generator(device=device).manual_seed(4000)
+    for N, K in ((4096, 4096), (11008, 4096), (4096, 11008)):
+        w = (torch.randn((N, K), device=device, generator=gen) * 0.02).half().float()
+        s = torch.randn((N, K), device=device, generator=gen) ** 2
+        quantize.seed_and_upscale_layer(w, s)                                  # warm-up (module load, allocations)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        luts, codes = quantize.seed_and_upscale_layer(w, s)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        rows = 4
+        wn, sn = w[:rows].cpu().numpy(), s[:rows].cpu().numpy()
+        t0 = time.perf_counter()
+        ref_luts, ref_codes = su.seed_and_upscale_layer(wn, sn, 3, 8, blocked=True)
+        cpu_s = (time.perf_counter() - t0) / rows
+        same = bool(np.array_equal(codes[:rows].cpu().numpy(), ref_codes)) and all(
+            np.array_equal(luts[bit][:rows].cpu().numpy().view(np.uint16), ref_luts[bit].view(np.uint16)) for bit in ref_luts)
+        out[f"{N}x{K}"] = {"gpu_ms": round(ms, 2), "rows_per_s": round(N / ms * 1e3), "weights_per_s": round(N * K / ms * 1e3),
+                           "cpu_checker_rows_per_s_one_core": round(1.0 / cpu_s, 1), "first_rows_equal_checker": same}
+    return {"what": "seed 3-bit + upscale to 8-bit per-row tables and codes (quantize.py:85-187 of the reference), fp32 in, "
+                    "fp16-valued N(0, 0.02) weights, squared-normal sensitivities", "layers": out}
 
 
 # ------------------------------------------------------------------------------------- whole-model decode

@@ -248,6 +248,27 @@ int ap_decode_attention(const void* qkv, int q_row_stride, const void* k_cache, 
                         void* out, int sequences, int heads, int kv_heads, int head_dim, int max_seq, float scale,
                         int splits, void* scratch, void* stream);
 
+/*
+ * Seed + incremental-upscale quantisation of a weight matrix, one thread block per row.  Replaces the
+ * reference's CPU routine any_precision/quantization/quantize.py:85-187 (_seed_and_upscale_layer, numba) with
+ * its helpers :13-76 and the two 1-D k-means routines it takes from the flash1dkmeans package (restated with
+ * a deterministic start; see the kernel's file header).  group_count = 1 only (one table per row), as the
+ * reference's packer requires (pack.py:126-127).
+ *   weight, sensitivity  fp32 [N][K] (sensitivity = the sample weights, e.g. squared gradients; >= 0)
+ *   codes                uint8 [N][K]: parent_bits-bit cluster index of every weight; its top b bits index
+ *                        the b-bit table
+ *   luts                 fp16: for b = seed_bits .. parent_bits in turn a table [N][2^b], one after the other
+ *                        (N * (2^(parent_bits + 1) - 2^seed_bits) halfs in all), ascending along a row
+ *   max_iter             Lloyd assignments of the seed k-means (the reference passes 50, quantize.py:148)
+ *   workspace            8-byte aligned device memory, ap_seed_upscale_workspace_bytes(K, blocks) bytes for
+ *                        `blocks` rows in flight; the call runs min(N, workspace_bytes / (16 K)) blocks
+ * 1 <= seed_bits <= parent_bits <= 8; K <= 32768 (a row is sorted in shared memory), else AP_ERR_UNSUPPORTED.
+ * Weights must be finite.  Equal values keep their original order in the sort.
+ */
+size_t ap_seed_upscale_workspace_bytes(int K, int blocks);
+int ap_seed_upscale(const void* weight, const void* sensitivity, int N, int K, int seed_bits, int parent_bits,
+                    int max_iter, void* codes, void* luts, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
