@@ -68,6 +68,10 @@ def load_library() -> ctypes.CDLL:
     lib.ap_matmul_kbit_splitk.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, vp]
     lib.ap_matmul_kbit_gated.restype = i
     lib.ap_matmul_kbit_gated.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, vp]
+    lib.ap_matmul_kbit_prenorm.restype = i
+    lib.ap_matmul_kbit_prenorm.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, i, vp, i, i, ctypes.c_float, vp]
+    lib.ap_matmul_kbit_residual.restype = i
+    lib.ap_matmul_kbit_residual.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, vp, vp, vp, vp]
     lib.ap_silu_mul.restype = i
     lib.ap_silu_mul.argtypes = [vp, vp, i, i, i, vp]
     lib.ap_gemm_kbit.restype = i
@@ -255,7 +259,8 @@ def reserve_workspace(device=None, nbytes: int = _MIN_WORKSPACE) -> int:
 
 
 def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bits: int, *,
-                out: torch.Tensor | None = None, splits: int | None = None, gated: bool = False):
+                out: torch.Tensor | None = None, splits: int | None = None, gated: bool = False,
+                prenorm=None, residual=None):
     """``x @ W_w.T`` for fp16 ``x[..., K]``; returns fp16 ``[..., N]``.
 
     Same call as the reference's ``matmul_kbit`` (kernels/main.cu:93-143).  ``splits`` (default:
@@ -264,6 +269,11 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
     ``gated=True`` (no counterpart in the reference): the operand holds a gated MLP's gate and up
     projections stacked tile by tile (``packing.interleave_gate_up``) and the result is
     ``silu(gate) * up`` of shape ``[..., N / 2]``; at most eight rows, fast-kernel shapes only.
+    ``residual=(h, norm_weight, ssq)`` and ``prenorm=(ssq, width, eps)`` (no counterpart either) fold a
+    pre-norm decoder's residual add and RMSNorm into a pair of products: the first adds its result to
+    ``h`` in place, returns ``h * norm_weight`` and leaves per-tile sums of squares in ``ssq`` (fp32
+    ``[rows, N / 16]``); the second takes that as ``x`` and scales its result by
+    ``rsqrt(sum(ssq) / width + eps)`` (``ap_matmul_kbit_residual`` / ``ap_matmul_kbit_prenorm``).
     """
     N, K, plane_stride = _check_operands(qweight, lut, w_bits)
     if x.dtype != torch.float16:
@@ -295,7 +305,23 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
         if splits is None:
             splits = _pick_splits(x.device, N, K)
         ws = _workspace(lib, x.device, stream, M, N, splits) if splits > 1 else None
-        if gated:
+        wsp, wsn, nsp = (ws.data_ptr(), ws.numel(), splits) if ws is not None else (None, 0, 1)
+        if residual is not None:
+            h, norm_w, ssq = residual
+            if gated or prenorm is not None or h.shape != out.shape or h.dtype != torch.float16 or not h.is_contiguous() \
+                    or norm_w.dtype != torch.float16 or norm_w.numel() != N or ssq.dtype != torch.float32 \
+                    or ssq.numel() < M * (N // 16) or N % 16 or M > 8:
+                raise ValueError("residual=(h [..., N] fp16, norm_weight [N] fp16, ssq fp32 [rows * N / 16]), at most eight rows")
+            rc = lib.ap_matmul_kbit_residual(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),
+                                             M, N, K, w_bits, nsp, wsp, wsn, h.data_ptr(), norm_w.data_ptr(), ssq.data_ptr(), stream)
+        elif prenorm is not None:
+            ssq, width, eps = prenorm
+            if ssq.dtype != torch.float32 or width % 16 or ssq.numel() < M * (width // 16):
+                raise ValueError("prenorm=(ssq fp32 [rows * width / 16], width, eps)")
+            rc = lib.ap_matmul_kbit_prenorm(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),
+                                            M, N, K, w_bits, nsp, wsp, wsn, 1 if gated else 0, ssq.data_ptr(), width // 16,
+                                            width, eps, stream)
+        elif gated:
             rc = lib.ap_matmul_kbit_gated(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),
                                           M, N, K, w_bits, splits if ws is not None else 1,
                                           ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)

@@ -17,8 +17,8 @@ reference leaves open:
 * a decode step reads its position from device memory, so one CUDA graph per precision is captured
   once and replayed for every generated token.
 
-Attention over the static KV cache is ``ap_decode_attention`` for a decode step (one query per sequence,
-grouped-query heads, fp32 softmax) and ``torch.nn.functional.scaled_dot_product_attention`` for the
+Attention over the static KV cache is ``ap_decode_attention_rope`` for a decode step (one query per sequence,
+grouped-query heads, fp32 softmax; it rotates q and k and stores the new k and v itself) and ``torch.nn.functional.scaled_dot_product_attention`` for the
 prompt; ``lm_head`` and the embeddings stay fp16, as in the reference (only the modules its
 architecture files name are quantised, any_precision/analyzer/architectures/llama.yaml:5-12).
 Greedy sampling only; batch size fixed at construction.
@@ -82,6 +82,8 @@ def _ops():
     lib.ap_rope_cache.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, vp]
     lib.ap_decode_attention.restype = i
     lib.ap_decode_attention.argtypes = [vp, i, vp, vp, vp, vp, i, i, i, i, i, f, i, vp, vp]
+    lib.ap_decode_attention_rope.restype = i
+    lib.ap_decode_attention_rope.argtypes = [vp, i, vp, vp, vp, vp, vp, i, i, i, i, i, f, i, vp, vp]
     lib.ap_decode_attention_scratch_bytes.restype = ctypes.c_size_t
     lib.ap_decode_attention_scratch_bytes.argtypes = [i, i, i, i]
     lib._decoder_ready = True
@@ -180,6 +182,7 @@ class AnyPrecisionLlama:
         self.h = torch.empty((batch, s.hidden), dtype=torch.float16, device=dev)
         self.y = torch.empty_like(self.h)
         self.act = torch.empty((batch, self.ffn), dtype=torch.float16, device=dev)
+        self.ssq = torch.zeros((batch, s.hidden // 16), dtype=torch.float32, device=dev)     # per-tile sums of squares of h
         self.attn = torch.empty((batch, self.heads * s.head_dim), dtype=torch.float16, device=dev)
         # a decode step has few heads: cut each head's cached positions over enough blocks for about two per SM
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -189,6 +192,7 @@ class AnyPrecisionLlama:
             nbytes = self.lib.ap_decode_attention_scratch_bytes(batch, self.heads, s.head_dim, self.attn_splits)
             self.attn_scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         self._graphs = {}
+        self.fold_norms = True                              # False: every norm a launch of its own (the prompt's path)
         self._side = None                                   # the stream decode graphs are captured and replayed on
 
     # ------------------------------------------------------------------------------------ construction
@@ -355,24 +359,68 @@ class AnyPrecisionLlama:
             return last @ self.lm_head.T
 
     # ------------------------------------------------------------------------------------ decode
+    def _attention(self, L, qkv):
+        """Rotary embedding of q and k, the cache write and the attention itself: one launch."""
+        s = self.spec
+        _check(self.lib, self.lib.ap_decode_attention_rope(
+            qkv.data_ptr(), qkv.shape[1], self.cos_sin.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),
+            self.pos.data_ptr(), self.attn.data_ptr(), self.batch, self.heads, self.kv_heads, s.head_dim, self.max_seq,
+            1.0 / math.sqrt(s.head_dim), self.attn_splits,
+            self.attn_scratch.data_ptr() if self.attn_scratch is not None else None, self._stream()),
+            "ap_decode_attention_rope")
+
+    def _folded_norms(self):
+        """Whether a decode step can fold every residual add + RMSNorm into the products around it: one GPU
+        (a row-parallel output must be summed over the ranks before it is added), at most eight sequences,
+        shapes the decode kernel takes."""
+        if self.tp_world != 1 or self.batch > 8:
+            return False
+        return all(m.bias is None and m.in_features % 128 == 0 and m.out_features % 16 == 0
+                   for L in self.layers for m in (L.qkv, L.o, L.gate_up, L.down))
+
+    def _decode_step_folded(self):
+        """The decode step with five launches per layer: q+k+v (scaled by the norm's rsqrt in its epilogue),
+        attention (rotation and cache write inside), o (residual add, norm weights and sums of squares in its
+        epilogue), gate+up (scaled, SiLU * up in its epilogue), down (as o, with the next layer's norm).  The
+        first norm is the stand-alone kernel; the last one's scale is positive and the same for all logits of a
+        sequence, so the arg-max needs none."""
+        s = self.spec
+        h, y, ssq = self.h, self.y, self.ssq
+        h.copy_(self.embed[self.tok])
+        self._add_rmsnorm(h, None, self.layers[0].in_norm, y)
+        for li, L in enumerate(self.layers):
+            qkv = L.qkv(y) if li == 0 else L.qkv.forward_prenorm(y, ssq, s.hidden, s.rms_eps)
+            self._attention(L, qkv)
+            L.o.forward_residual(self.attn, h, L.post_norm, ssq, out=y)
+            L.gate_up.forward_prenorm(y, ssq, s.hidden, s.rms_eps, out=self.act)
+            nxt = self.layers[li + 1].in_norm if li + 1 < len(self.layers) else self.final_norm
+            L.down.forward_residual(self.act, h, nxt, ssq, out=y)
+        logits = y @ self.lm_head.T
+        self.tok.copy_(logits.argmax(dim=-1))
+        self.pos.add_(1)
+
+    @torch.inference_mode()
+    def last_logits(self) -> torch.Tensor:
+        """fp32 logits ``[batch, vocab]`` of the decode step that ran last (the step itself keeps only their
+        arg-max).  After a step with folded norms ``self.y`` is the residual stream times the last norm's
+        weights without the division by its root mean square, which is applied here."""
+        y = self.y.float()
+        if self.fold_norms and self._folded_norms():
+            y = y * torch.rsqrt(self.h.float().pow(2).mean(-1, keepdim=True) + self.spec.rms_eps)
+        return y @ self.lm_head.float().T
+
     def _decode_step(self):
         """One token per sequence: reads ``self.tok`` and ``self.pos``, writes the next token to ``self.tok``
         and advances ``self.pos``.  Everything it touches lives on the device (graph-replayable)."""
+        if self.fold_norms and self._folded_norms():
+            return self._decode_step_folded()
         s, B = self.spec, self.batch
         self.h.copy_(self.embed[self.tok])
         mlp = None
         for L in self.layers:
             self._add_rmsnorm(self.h, mlp, L.in_norm, self.y)
             qkv = L.qkv(self.y)                                              # decode kernel: B <= 8 rows
-            _check(self.lib, self.lib.ap_rope_cache(qkv.data_ptr(), self.cos_sin.data_ptr(), self.pos.data_ptr(),
-                                                    L.k_cache.data_ptr(), L.v_cache.data_ptr(), B, 1, self.heads, self.kv_heads,
-                                                    s.head_dim, self.max_seq, self._stream()), "ap_rope_cache")
-            _check(self.lib, self.lib.ap_decode_attention(qkv.data_ptr(), qkv.shape[1], L.k_cache.data_ptr(),
-                                                          L.v_cache.data_ptr(), self.pos.data_ptr(), self.attn.data_ptr(), B,
-                                                          self.heads, self.kv_heads, s.head_dim, self.max_seq,
-                                                          1.0 / math.sqrt(s.head_dim), self.attn_splits,
-                                                          self.attn_scratch.data_ptr() if self.attn_scratch is not None else None,
-                                                          self._stream()), "ap_decode_attention")
+            self._attention(L, qkv)
             mlp = self._layer_tail(L, self.h, self.y, self.attn, decode=True)
         self._add_rmsnorm(self.h, mlp, self.final_norm, self.y)
         logits = self.y @ self.lm_head.T

@@ -187,6 +187,30 @@ class AnyPrecisionLinear(nn.Module):
         gu = self.forward(x, **kwargs)
         return _ext.silu_mul(gu, tiled=True, out=out)
 
+    def _decode_operands(self, x, kwargs):
+        w_bits = kwargs['precision'] if 'precision' in kwargs else self.precision
+        lut = self._buffers.get(f'lut{w_bits}')
+        if lut is None:
+            raise RuntimeError(f'{w_bits}-bit table is not loaded; available: {self.precisions}')
+        if self.bias is not None or not _ext.gated_supported(x, self.qweight, lut):
+            raise RuntimeError('the fused decoder products need up to eight rows, no bias, and operands the decode kernel takes')
+        return w_bits, lut
+
+    def forward_residual(self, x, h, norm_weight, ssq, out=None, **kwargs):
+        """``h += self(x)`` in place; returns ``h * norm_weight`` (not yet normalised) and leaves the per-tile
+        sums of squares of the new ``h`` in ``ssq``: the first half of a folded residual add + RMSNorm
+        (``any_precision_ext.matmul_kbit(residual=)``)."""
+        w_bits, lut = self._decode_operands(x, kwargs)
+        return _ext.matmul_kbit(x, self.qweight, lut, w_bits, out=out, residual=(h, norm_weight, ssq))
+
+    def forward_prenorm(self, x, ssq, width, eps, out=None, **kwargs):
+        """``self(rmsnorm-scaled x)`` for the ``x`` and ``ssq`` that ``forward_residual`` of the previous layer
+        left (``width`` = that layer's ``out_features``); with a ``fuse_gated`` module the result is
+        ``silu(gate) * up``."""
+        w_bits, lut = self._decode_operands(x, kwargs)
+        return _ext.matmul_kbit(x, self.qweight, lut, w_bits, out=out, gated=getattr(self, 'gated', False),
+                                prenorm=(ssq, width, eps))
+
     def forward_split(self, x, **kwargs):
         """``forward`` of a fused module, cut back into the original layers' outputs (views)."""
         return torch.split(self.forward(x, **kwargs), getattr(self, 'split_sizes', [self.out_features]), dim=-1)

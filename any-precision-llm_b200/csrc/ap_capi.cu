@@ -73,7 +73,8 @@ size_t ticket_bytes(int) { return kTicketAreaBytes; }
 bool tickets_fit(int N) { return static_cast<size_t>((N + 15) / 16) * sizeof(int) <= kTicketAreaBytes; }
 
 int matmul_impl(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out, int M, int N,
-                int K, int w_bits, int splits, void* workspace, size_t workspace_bytes, void* stream, int gated = 0) {
+                int K, int w_bits, int splits, void* workspace, size_t workspace_bytes, void* stream,
+                const ap::GemvEpilogue* epi = nullptr) {
     int rc = check_common(qweight, plane_stride, lut, out, N, K, w_bits);
     if (rc != AP_OK) return rc;
     if (!x) return AP_ERR_NULL_POINTER;
@@ -94,7 +95,7 @@ int matmul_impl(const void* x, const void* qweight, int64_t plane_stride, const 
     char* op = static_cast<char*>(out);
     // eight batch rows per pass over the planes; the launcher runs the passes (side by side where it can)
     cudaError_t e = ap::launch_gemv(xp, qweight, plane_stride, lut, op, M, N, K, w_bits, splits, partials, tickets,
-                                    static_cast<cudaStream_t>(stream), gated);
+                                    static_cast<cudaStream_t>(stream), epi);
     if (e == cudaErrorNotSupported) return AP_ERR_UNSUPPORTED;
     return e == cudaSuccess ? AP_OK : cuda_fail(e);
 }
@@ -122,7 +123,41 @@ extern "C" int ap_matmul_kbit_gated(const void* x, const void* qweight, int64_t 
                                     int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
                                     void* stream) {
     if (splits < 1 || N % 16 != 0 || M > 8) return M > 8 || N % 16 ? AP_ERR_UNSUPPORTED : AP_ERR_BAD_SHAPE;
-    return matmul_impl(x, qweight, plane_stride, lut, out, M, N, K, w_bits, splits, workspace, workspace_bytes, stream, 1);
+    ap::GemvEpilogue epi = {};
+    epi.mode = 1;
+    return matmul_impl(x, qweight, plane_stride, lut, out, M, N, K, w_bits, splits, workspace, workspace_bytes, stream, &epi);
+}
+
+extern "C" int ap_matmul_kbit_prenorm(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out,
+                                      int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
+                                      int gated, const void* ssq, int ssq_blocks, int width, float eps, void* stream) {
+    if (!ssq) return AP_ERR_NULL_POINTER;
+    if (splits < 1 || ssq_blocks < 1 || width < 1) return AP_ERR_BAD_SHAPE;
+    if (N % 16 != 0 || M > 8) return AP_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(ssq) & 3) return AP_ERR_BAD_ALIGNMENT;
+    ap::GemvEpilogue epi = {};
+    epi.mode = gated ? 3 : 2;
+    epi.ssq_in = static_cast<const float*>(ssq);
+    epi.ssq_blocks = ssq_blocks;
+    epi.inv_width = 1.0f / static_cast<float>(width);
+    epi.eps = eps;
+    return matmul_impl(x, qweight, plane_stride, lut, out, M, N, K, w_bits, splits, workspace, workspace_bytes, stream, &epi);
+}
+
+extern "C" int ap_matmul_kbit_residual(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out,
+                                       int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
+                                       void* resid, const void* norm_weight, void* ssq_out, void* stream) {
+    if (!resid || !norm_weight || !ssq_out) return AP_ERR_NULL_POINTER;
+    if (splits < 1) return AP_ERR_BAD_SHAPE;
+    if (N % 16 != 0 || M > 8) return AP_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(norm_weight)) & 1 || reinterpret_cast<uintptr_t>(ssq_out) & 3)
+        return AP_ERR_BAD_ALIGNMENT;
+    ap::GemvEpilogue epi = {};
+    epi.mode = 4;
+    epi.resid = static_cast<__half*>(resid);
+    epi.norm_w = static_cast<const __half*>(norm_weight);
+    epi.ssq_out = static_cast<float*>(ssq_out);
+    return matmul_impl(x, qweight, plane_stride, lut, out, M, N, K, w_bits, splits, workspace, workspace_bytes, stream, &epi);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -11,7 +11,8 @@
 //   ap_rope_cache    rotary embedding of q and k at each row's position, k and v written into the
 //                    KV cache at that position                                           one block per row
 //   ap_silu_mul      y = silu(gate) * up for gate|up side by side or tile by tile         grid-stride
-//   ap_decode_attention  one query per sequence against its KV cache up to the query's position
+//   ap_decode_attention  (and ap_decode_attention_rope, which rotates q and k and writes the cache itself)
+//                    one query per sequence against its KV cache up to the query's position
 //                    (grouped-query heads), softmax in fp32                              one block per (head, sequence)
 // All fp16 in and out with fp32 arithmetic.  Positions come from device memory, so that a captured
 // CUDA graph can be replayed for every step of a generation.
@@ -89,6 +90,11 @@ add_rmsnorm_kernel(__half* __restrict__ h, const __half* __restrict__ delta, con
     for (int i = (threadIdx.x + kKeep * nthr) * 2; i < hidden; i += nthr * 2) emit(i, *reinterpret_cast<const __half2*>(hr + i));
 }
 
+// One rotated pair (x[i], x[i + head_dim / 2]) -> (a c - b s, b c + a s), every product and sum rounded on its
+// own so that the stand-alone kernel and the attention kernel that rotates on the fly give the same bits.
+__device__ __forceinline__ float rot_lo(float a, float b, float c, float s) { return __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)); }
+__device__ __forceinline__ float rot_hi(float a, float b, float c, float s) { return __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)); }
+
 // qkv: [rows][(heads + 2 kv_heads) * head_dim] = q | k | v of one token per row.  Rotates q in place
 // (pairs (i, i + head_dim/2), the "rotate half" convention) and writes rotated k and plain v into the
 // caches [sequences][kv_heads][max_seq][head_dim] at position pos[row] of sequence row / rows_per_seq.
@@ -110,7 +116,7 @@ rope_cache_kernel(__half* __restrict__ qkv, const float* __restrict__ cos_sin, c
         for (int i = threadIdx.x; i < half_dim; i += blockDim.x) {
             const float a = __half2float(base[i]), b = __half2float(base[i + half_dim]);
             const float c = cs[i], s = cs[half_dim + i];
-            const __half ra = __float2half_rn(a * c - b * s), rb = __float2half_rn(b * c + a * s);
+            const __half ra = __float2half_rn(rot_lo(a, b, c, s)), rb = __float2half_rn(rot_hi(a, b, c, s));
             if (slot < heads) {
                 base[i] = ra;
                 base[i + half_dim] = rb;
@@ -153,11 +159,18 @@ silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ y, int 
 // Each block parks (maximum, sum, unnormalised vector) in `scratch`; the block that draws the last ticket of a
 // (head, sequence) merges the ranges in index order, writes fp16 and hands the ticket back at zero.  fp32
 // throughout.
-template <int D>
+//
+// ROPE: the rows of `qkv` are the raw q | k | v of the new token (position pos[b]), the caches hold the earlier
+// positions only.  The block rotates its q on the fly; the one thread that owns position pos[b] takes k from
+// `qkv`, rotates it and (in the first query head of a KV group) stores it in the cache; v of that position is
+// read from `qkv` and stored likewise.  No block reads position pos[b] from the caches, so the writes race with
+// nothing in this launch.  Rounding as in rope_cache_kernel followed by the plain kernel.
+template <int D, bool ROPE>
 __global__ void __launch_bounds__(256)
-decode_attention_kernel(const __half* __restrict__ qkv, int q_row_stride, const __half* __restrict__ k_cache,
-                        const __half* __restrict__ v_cache, const int* __restrict__ pos, __half* __restrict__ out, int heads,
-                        int kv_heads, int max_seq, float scale, float* __restrict__ scratch, int* __restrict__ tickets) {
+decode_attention_kernel(const __half* __restrict__ qkv, int q_row_stride, const __half* k_cache, const __half* v_cache,
+                        const int* __restrict__ pos, __half* __restrict__ out, int heads, int kv_heads, int max_seq, float scale,
+                        float* __restrict__ scratch, int* __restrict__ tickets, const float* __restrict__ cos_sin,
+                        __half* k_cache_w, __half* v_cache_w) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int kThreads = 256, kTile = kThreads;
@@ -174,12 +187,41 @@ decode_attention_kernel(const __half* __restrict__ qkv, int q_row_stride, const 
     const __half* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_seq * D;
     const __half* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_seq * D;
     __shared__ float sq[D];
+    __shared__ __align__(16) __half sk[D];                   // ROPE: the new token's rotated k
     __shared__ float sw[kTile];
     __shared__ float red[8];
     __shared__ float sacc[kGroups][D];
     __shared__ int s_last;
-    for (int i = tid; i < D; i += kThreads) sq[i] = __half2float(qkv[(size_t)b * q_row_stride + (size_t)h * D + i]) * scale;
+    // the new token's position, if this launch brings it along and it lies inside the cache
+    const int pn = (ROPE && pos[b] >= 0 && pos[b] < max_seq) ? pos[b] : -1;
+    const bool writer = ROPE && (h % (heads / kv_heads)) == 0;
+    const __half* vraw = qkv + (size_t)b * q_row_stride + (size_t)(heads + kv_heads + kvh) * D;
+    if (ROPE && pn >= 0) {
+        const float* cs = cos_sin + (size_t)pn * D;
+        const __half* qr = qkv + (size_t)b * q_row_stride + (size_t)h * D;
+        for (int i = tid; i < D; i += kThreads) {
+            const int j = i < D / 2 ? i : i - D / 2;
+            const float a = __half2float(qr[j]), bq = __half2float(qr[j + D / 2]);
+            const float r = i < D / 2 ? rot_lo(a, bq, cs[j], cs[D / 2 + j]) : rot_hi(a, bq, cs[j], cs[D / 2 + j]);
+            sq[i] = __half2float(__float2half_rn(r)) * scale;
+        }
+        if (pn >= p_begin && pn < p_end) {                   // this block's range holds the new position
+            const __half* kraw = qkv + (size_t)b * q_row_stride + (size_t)(heads + kvh) * D;
+            for (int i = tid; i < D / 2; i += kThreads) {
+                const float a = __half2float(kraw[i]), bk = __half2float(kraw[i + D / 2]);
+                sk[i] = __float2half_rn(rot_lo(a, bk, cs[i], cs[D / 2 + i]));
+                sk[i + D / 2] = __float2half_rn(rot_hi(a, bk, cs[i], cs[D / 2 + i]));
+            }
+        }
+    } else {
+        for (int i = tid; i < D; i += kThreads) sq[i] = __half2float(qkv[(size_t)b * q_row_stride + (size_t)h * D + i]) * scale;
+    }
     __syncthreads();
+    if (ROPE && writer && pn >= p_begin && pn < p_end && tid < D / 8) {
+        const size_t at = (((size_t)b * kv_heads + kvh) * max_seq + pn) * D;
+        reinterpret_cast<uint4*>(k_cache_w + at)[tid] = reinterpret_cast<const uint4*>(sk)[tid];
+        reinterpret_cast<uint4*>(v_cache_w + at)[tid] = reinterpret_cast<const uint4*>(vraw)[tid];
+    }
     const int dt = tid % kDT, grp = tid / kDT;
     float m = -INFINITY, l = 0.f;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -194,16 +236,23 @@ decode_attention_kernel(const __half* __restrict__ qkv, int q_row_stride, const 
         uint4 vpre[kPre];
         float s = -INFINITY;
         uint4 kv[D / 8];
-        if (p < p_end) {
+        if (ROPE && p == pn && p < p_end) {                  // the new token's rotated k waits in shared memory
+#pragma unroll
+            for (int i = 0; i < D / 8; i++) kv[i] = reinterpret_cast<const uint4*>(sk)[i];
+        } else if (p < p_end) {
             const uint4* row = reinterpret_cast<const uint4*>(kb + (size_t)p * D);
 #pragma unroll
             for (int i = 0; i < D / 8; i++) kv[i] = row[i];
         }
+        // row of v at cached position q2: the new token's comes from `qkv`
+        auto v_row = [&](int q2) {
+            return reinterpret_cast<const uint4*>((ROPE && q2 == pn) ? vraw + 8 * dt : vb + (size_t)q2 * D + 8 * dt);
+        };
         if (pre) {
 #pragma unroll
             for (int i = 0; i < kPre; i++) {
                 const int j = grp + i * kGroups;
-                vpre[i] = (j < cnt) ? *reinterpret_cast<const uint4*>(vb + (size_t)(t0 + j) * D + 8 * dt) : make_uint4(0u, 0u, 0u, 0u);
+                vpre[i] = (j < cnt) ? *v_row(t0 + j) : make_uint4(0u, 0u, 0u, 0u);
             }
         }
         if (p < p_end) {
@@ -258,7 +307,7 @@ decode_attention_kernel(const __half* __restrict__ qkv, int q_row_stride, const 
             }
         } else {
 #pragma unroll 4
-            for (int j = grp; j < cnt; j += kGroups) add_row(*reinterpret_cast<const uint4*>(vb + (size_t)(t0 + j) * D + 8 * dt), sw[j]);
+            for (int j = grp; j < cnt; j += kGroups) add_row(*v_row(t0 + j), sw[j]);
         }
         __syncthreads();                                     // sw[] and red[] are rewritten by the next tile
     }
@@ -361,34 +410,64 @@ extern "C" size_t ap_decode_attention_scratch_bytes(int sequences, int heads, in
     return tickets + (size_t)sequences * heads * splits * (head_dim + 2) * sizeof(float);
 }
 
-extern "C" int ap_decode_attention(const void* qkv, int q_row_stride, const void* k_cache, const void* v_cache,
-                                   const void* pos, void* out, int sequences, int heads, int kv_heads, int head_dim,
-                                   int max_seq, float scale, int splits, void* scratch, void* stream) {
+namespace {
+
+int decode_attention_impl(const void* qkv, int q_row_stride, const void* cos_sin, void* k_cache, void* v_cache, const void* pos,
+                          void* out, int sequences, int heads, int kv_heads, int head_dim, int max_seq, float scale, int splits,
+                          void* scratch, void* stream) {
     if (!qkv || !k_cache || !v_cache || !pos || !out) return AP_ERR_NULL_POINTER;
-    if (sequences < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads || max_seq < 1 || q_row_stride < heads * head_dim ||
+    const int need_stride = cos_sin ? (heads + 2 * kv_heads) * head_dim : heads * head_dim;
+    if (sequences < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads || max_seq < 1 || q_row_stride < need_stride ||
         splits < 1 || splits > 64)
         return AP_ERR_BAD_SHAPE;
     if (splits > 1 && !scratch) return AP_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
-         reinterpret_cast<uintptr_t>(scratch)) & 15)
+         reinterpret_cast<uintptr_t>(scratch) | reinterpret_cast<uintptr_t>(cos_sin)) & 15)
         return AP_ERR_BAD_ALIGNMENT;
+    if (cos_sin && (q_row_stride % 8 || head_dim % 16)) return AP_ERR_BAD_ALIGNMENT;     // 16-byte rows of raw k and v
     const dim3 grid(heads, sequences, splits), block(256);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto q = static_cast<const __half*>(qkv);
     auto k = static_cast<const __half*>(k_cache);
     auto v = static_cast<const __half*>(v_cache);
+    auto kw = static_cast<__half*>(k_cache);
+    auto vw = static_cast<__half*>(v_cache);
     auto p = static_cast<const int*>(pos);
     auto o = static_cast<__half*>(out);
+    auto cs = static_cast<const float*>(cos_sin);
     int* tickets = static_cast<int*>(scratch);
     const size_t ticket_bytes = ((size_t)sequences * heads * sizeof(int) + 255) & ~static_cast<size_t>(255);
     float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + ticket_bytes) : nullptr;
     cudaError_t e;
+#define AP_ATTN(D_)                                                                                                              \
+    e = cos_sin ? launch_pdl(decode_attention_kernel<D_, true>, grid, block, st, q, q_row_stride, k, v, p, o, heads, kv_heads,   \
+                             max_seq, scale, partials, tickets, cs, kw, vw)                                                      \
+                : launch_pdl(decode_attention_kernel<D_, false>, grid, block, st, q, q_row_stride, k, v, p, o, heads, kv_heads,  \
+                             max_seq, scale, partials, tickets, cs, kw, vw)
     switch (head_dim) {
-        case 32: e = launch_pdl(decode_attention_kernel<32>, grid, block, st, q, q_row_stride, k, v, p, o, heads, kv_heads, max_seq, scale, partials, tickets); break;
-        case 64: e = launch_pdl(decode_attention_kernel<64>, grid, block, st, q, q_row_stride, k, v, p, o, heads, kv_heads, max_seq, scale, partials, tickets); break;
-        case 128: e = launch_pdl(decode_attention_kernel<128>, grid, block, st, q, q_row_stride, k, v, p, o, heads, kv_heads, max_seq, scale, partials, tickets); break;
-        case 256: e = launch_pdl(decode_attention_kernel<256>, grid, block, st, q, q_row_stride, k, v, p, o, heads, kv_heads, max_seq, scale, partials, tickets); break;
+        case 32: AP_ATTN(32); break;
+        case 64: AP_ATTN(64); break;
+        case 128: AP_ATTN(128); break;
+        case 256: AP_ATTN(256); break;
         default: return AP_ERR_UNSUPPORTED;
     }
+#undef AP_ATTN
     return e == cudaSuccess ? AP_OK : AP_ERR_LAUNCH;
+}
+
+}  // namespace
+
+extern "C" int ap_decode_attention(const void* qkv, int q_row_stride, const void* k_cache, const void* v_cache,
+                                   const void* pos, void* out, int sequences, int heads, int kv_heads, int head_dim,
+                                   int max_seq, float scale, int splits, void* scratch, void* stream) {
+    return decode_attention_impl(qkv, q_row_stride, nullptr, const_cast<void*>(k_cache), const_cast<void*>(v_cache), pos, out,
+                                 sequences, heads, kv_heads, head_dim, max_seq, scale, splits, scratch, stream);
+}
+
+extern "C" int ap_decode_attention_rope(const void* qkv, int q_row_stride, const void* cos_sin, void* k_cache, void* v_cache,
+                                        const void* pos, void* out, int sequences, int heads, int kv_heads, int head_dim,
+                                        int max_seq, float scale, int splits, void* scratch, void* stream) {
+    if (!cos_sin) return AP_ERR_NULL_POINTER;
+    return decode_attention_impl(qkv, q_row_stride, cos_sin, k_cache, v_cache, pos, out, sequences, heads, kv_heads, head_dim,
+                                 max_seq, scale, splits, scratch, stream);
 }

@@ -558,7 +558,7 @@ gemv_kbit_plain_kernel(const __half* __restrict__ x, const uint32_t* __restrict_
 template <int W>
 static cudaError_t launch_w(const void* x, const void* q, long long plane_stride, const void* lut, void* out, int M,
                             int N, int K, bool fast, int splits, float* partials, int* tickets, cudaStream_t stream,
-                            int gated = 0) {
+                            const GemvEpilogue* epi = nullptr) {
     auto xp = static_cast<const __half*>(x);
     auto qp = static_cast<const uint32_t*>(q);
     auto lp = static_cast<const uint16_t*>(lut);
@@ -569,11 +569,11 @@ static cudaError_t launch_w(const void* x, const void* q, long long plane_stride
         const char* e = getenv("AP_GEMV_LOADER");
         return !(e && e[0] == 'c');
     }();
-    if (gated) {
-        // silu(gate) * up in the epilogue: only the TMA kernel has it (decode batches, aligned operands)
+    if (epi) {
+        // the decoder's epilogues: only the TMA kernel has them (decode batches, aligned operands)
         if (!fast || !want_tma || M > 8) return cudaErrorNotSupported;
         bool used = false;
-        cudaError_t te = launch_tma<W>(xp, qp, plane_stride, lp, op, M, N, K, splits, partials, tickets, stream, &used, 1);
+        cudaError_t te = launch_tma<W>(xp, qp, plane_stride, lp, op, M, N, K, splits, partials, tickets, stream, &used, epi);
         return (used || te != cudaSuccess) ? te : cudaErrorNotSupported;
     }
     if (M > 8) {
@@ -654,17 +654,17 @@ bool gemv_fast_path(const void* x, const void* qweight, long long plane_stride, 
 
 cudaError_t launch_gemv(const void* x, const void* qweight, long long plane_stride, const void* lut, void* out,
                         int M, int N, int K, int w_bits, int splits, float* partials, int* tickets,
-                        cudaStream_t stream, int gated) {
+                        cudaStream_t stream, const GemvEpilogue* epi) {
     const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(qweight) |
                            reinterpret_cast<uintptr_t>(lut)) & 15) == 0;
     const bool fast = aligned && (K % 128 == 0) && (N % 16 == 0) && (plane_stride % 4 == 0);
     switch (w_bits) {
-        case 3: return launch_w<3>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, gated);
-        case 4: return launch_w<4>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, gated);
-        case 5: return launch_w<5>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, gated);
-        case 6: return launch_w<6>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, gated);
-        case 7: return launch_w<7>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, gated);
-        case 8: return launch_w<8>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, gated);
+        case 3: return launch_w<3>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, epi);
+        case 4: return launch_w<4>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, epi);
+        case 5: return launch_w<5>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, epi);
+        case 6: return launch_w<6>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, epi);
+        case 7: return launch_w<7>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, epi);
+        case 8: return launch_w<8>(x, qweight, plane_stride, lut, out, M, N, K, fast, splits, partials, tickets, stream, epi);
         default: return cudaErrorInvalidValue;
     }
 }

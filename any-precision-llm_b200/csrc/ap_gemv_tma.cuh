@@ -101,11 +101,80 @@ __device__ __forceinline__ void tensor_g2s_3d(uint32_t dst, const CUtensorMap* m
         : "memory");
 }
 
-template <int W, int OCC, int MODE, bool GATED = false>
+// ---------------------------------------------------------------------------------------------- the decoder's epilogues
+// Batch row `m`'s rsqrt(mean square + eps) from the per-tile sums of squares that the launch which wrote the
+// residual stream left behind, added in a fixed order (lane-strided, then a shuffle tree).  Called by warp m.
+__device__ __forceinline__ void dec_row_scale(const GemvEpilogue& epi, int m, int lane, float* rn_s) {
+    float ss = 0.f;
+    for (int i = lane; i < epi.ssq_blocks; i += 32) ss += __ldcg(epi.ssq_in + (size_t)m * epi.ssq_blocks + i);
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+    if (lane == 0) rn_s[m] = rsqrtf(ss * epi.inv_width + epi.eps);
+}
+
+// What becomes of a finished 16-row tile in the decoder's variants.  The fp32 product of tile row r with batch
+// row m is the sum of the eight warps' partial tiles in shared memory (`red`, S == 0) or of the S split-K
+// partials in the workspace.  Modes:
+//   1, 3  the 16 rows are eight gate rows followed by the eight up rows of the same features (a gated MLP's two
+//         projections stacked tile by tile); the tile's output is the eight values silu(gate) * up, rounded like
+//         the separate operations would be (both projections to fp16, the activation to fp16, then the product);
+//   2, 3  the activations were a residual stream times the norm weights, NOT yet divided by its root mean
+//         square: the products are scaled by rn_s[m] = rsqrt(mean square + eps) first (a matrix product commutes
+//         with a scale per batch row);
+//   4     residual update: resid[m][row] += fp16(product), and the output is the new residual times the next
+//         norm's weight, with this tile's sum of squares of the new residual in ssq_out[m][tile].
+__device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const float* red, const float* partials, int S, int M, int N,
+                                          int row0, __half* out, int tid, const float* rn_s, float pre_h, float pre_w) {
+    constexpr int kThreads = kGemvMaxWarps * 32;
+    auto total = [&](int m, int r) {
+        float sum = 0.f;
+        if (S == 0) {
+#pragma unroll
+            for (int w2 = 0; w2 < kGemvMaxWarps; w2++) sum += red[w2 * 128 + r * 8 + m];
+        } else {
+            for (int sp = 0; sp < S; sp++) sum += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r);
+        }
+        return sum;
+    };
+    const int mode = epi.mode;
+    if (mode == 1 || mode == 3) {
+        for (int i = tid; i < 8 * M; i += kThreads) {
+            const int m = i >> 3, r = i & 7;
+            float gs = total(m, r), us = total(m, r + 8);
+            if (mode == 3) { gs *= rn_s[m]; us *= rn_s[m]; }
+            const float gf = __half2float(__float2half_rn(gs)), uf = __half2float(__float2half_rn(us));
+            const float a = __half2float(__float2half_rn(gf / (1.f + __expf(-gf))));
+            out[(size_t)m * (N >> 1) + (row0 >> 1) + r] = __float2half_rn(a * uf);
+        }
+    } else if (mode == 2) {
+        for (int i = tid; i < 16 * M; i += kThreads) {
+            const int m = i >> 4, r = i & 15;
+            out[(size_t)m * N + row0 + r] = __float2half_rn(total(m, r) * rn_s[m]);
+        }
+    } else if (tid < 128) {                                  // mode 4; four whole warps: 16 lanes per batch row
+        const int m = tid >> 4, r = tid & 15;
+        float sq = 0.f;
+        if (m < M) {
+            const size_t at = (size_t)m * N + row0 + r;
+            const float o = __half2float(__float2half_rn(total(m, r)));
+            const __half hn = __float2half_rn(pre_h + o);    // the old residual and the norm weight were fetched early
+            epi.resid[at] = hn;
+            const float hf = __half2float(hn);
+            out[at] = __float2half_rn(hf * pre_w);
+            sq = hf * hf;
+        }
+#pragma unroll
+        for (int o2 = 8; o2 > 0; o2 >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o2);
+        if (m < M && r == 0) epi.ssq_out[(size_t)m * gridDim.x + blockIdx.x] = sq;
+    }
+}
+
+template <int W, int OCC, int MODE, bool DEC = false>
 __global__ void __launch_bounds__(kGemvMaxWarps * 32, OCC)
 gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __restrict__ x,
                      const uint16_t* __restrict__ lut, __half* __restrict__ out, int M, int N, int K, int mpad,
-                     int split_chunks, float* __restrict__ partials, int* __restrict__ tickets) {
+                     int split_chunks, float* __restrict__ partials, int* __restrict__ tickets,
+                     const __grid_constant__ GemvEpilogue epi) {
     using Cfg = GemvCfg<W>;
     using T = GemvTmaCfg<W, OCC, MODE>;
     constexpr int C = Cfg::C;
@@ -120,7 +189,10 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     unsigned char* bufs = smem;                                           // 1024-byte aligned boxes
     float* red = reinterpret_cast<float*>(smem + nbuf * buf_bytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(red) + Cfg::kRedBytes);   // full[nbuf][2]
-    // then empty[nbuf]: one arrival per warp that has finished its step of the buffer's chunk
+    // then empty[nbuf]: one arrival per warp that has finished its step of the buffer's chunk; the barriers take 96 of
+    // the 256 bytes kept for them, and the decoder variants keep eight floats at byte 128 (rsqrt(mean square + eps)
+    // per batch row)
+    float* rn_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 128);
 
     // More than eight batch rows (no split-K then): blockIdx.z takes rows [8 z, 8 z + 8) of x and out, so
     // that the passes over the planes run side by side in one launch and the later ones read them from L2.
@@ -294,6 +366,10 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     if (warp == 0) {
         for (int i = 0; i < first; i++) request_x(i);
     }
+    if constexpr (DEC) {
+        // by the warps that do not issue the copies, while the first chunks travel
+        if ((epi.mode == 2 || epi.mode == 3) && kGemvMaxWarps - 1 - warp < M) dec_row_scale(epi, kGemvMaxWarps - 1 - warp, lane, rn_s);
+    }
 
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const int total_steps = nchunks * 4;
@@ -389,6 +465,15 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     if (!ok && lane == 0) atomicExch(&ap_gemv_wait_expired, 1);
     AP_PROF(3);
 
+    // Mode 4 of the decoder variants: this thread's old residual and norm weight, requested before the reduction
+    // below so that their round trip hides behind it.
+    float pre_h = 0.f, pre_w = 0.f;
+    if constexpr (DEC) {
+        if (epi.mode == 4 && tid < 16 * M) {
+            pre_h = __half2float(epi.resid[(size_t)(tid >> 4) * N + row0 + (tid & 15)]);
+            pre_w = __half2float(epi.norm_w[row0 + (tid & 15)]);
+        }
+    }
     // Combine the warps' partial tiles: acc = {(g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)}.
     float* mine = red + warp * 128;
     mine[g * 8 + 2 * t] = acc[0][0] + acc[1][0];
@@ -396,31 +481,18 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     mine[(g + 8) * 8 + 2 * t] = acc[0][2] + acc[1][2];
     mine[(g + 8) * 8 + 2 * t + 1] = acc[0][3] + acc[1][3];
     __syncthreads();
-    // GATED: the 16 rows of a tile are eight gate rows followed by the eight up rows of the same
-    // features (a gated MLP's two projections stacked tile by tile), and the tile's output is the eight
-    // values silu(gate) * up, rounded like the separate operations would be (both projections to fp16,
-    // the activation to fp16, then the product).
-    auto gate = [](float gsum, float usum) {
-        const float gf = __half2float(__float2half_rn(gsum)), uf = __half2float(__float2half_rn(usum));
-        const float a = __half2float(__float2half_rn(gf / (1.f + __expf(-gf))));
-        return __float2half_rn(a * uf);
-    };
+    // What becomes of a finished 16-row tile: plain kernels round the fp32 products to fp16 and store them; the
+    // decoder's variants (DEC) hand them to dec_epilogue.
     if (gridDim.y == 1) {
-        if constexpr (!GATED) {
+        if constexpr (DEC) {
+            dec_epilogue(epi, red, nullptr, 0, M, N, row0, out, tid, rn_s, pre_h, pre_w);
+        } else {
             for (int i = tid; i < 16 * M; i += kThreads) {
                 const int m = i >> 4, r = i & 15;            // 16 consecutive rows per m: 32-byte stores
                 float sum = 0.f;
 #pragma unroll
                 for (int w2 = 0; w2 < kGemvMaxWarps; w2++) sum += red[w2 * 128 + r * 8 + m];
                 out[(size_t)m * N + row0 + r] = __float2half_rn(sum);
-            }
-        } else {
-            for (int i = tid; i < 8 * M; i += kThreads) {
-                const int m = i >> 3, r = i & 7;
-                float gs = 0.f, us = 0.f;
-#pragma unroll
-                for (int w2 = 0; w2 < kGemvMaxWarps; w2++) { gs += red[w2 * 128 + r * 8 + m]; us += red[w2 * 128 + (r + 8) * 8 + m]; }
-                out[(size_t)m * (N >> 1) + (row0 >> 1) + r] = gate(gs, us);
             }
         }
     } else {
@@ -441,22 +513,14 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
         __syncthreads();
         if (*flag) {
             __threadfence();
-            if constexpr (!GATED) {
+            if constexpr (DEC) {
+                dec_epilogue(epi, nullptr, partials, S, M, N, row0, out, tid, rn_s, pre_h, pre_w);
+            } else {
                 for (int i = tid; i < 16 * M; i += kThreads) {
                     const int m = i >> 4, r = i & 15;
                     float sum = 0.f;
                     for (int sp = 0; sp < S; sp++) sum += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r);
                     out[(size_t)m * N + row0 + r] = __float2half_rn(sum);
-                }
-            } else {
-                for (int i = tid; i < 8 * M; i += kThreads) {
-                    const int m = i >> 3, r = i & 7;
-                    float gs = 0.f, us = 0.f;
-                    for (int sp = 0; sp < S; sp++) {
-                        gs += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r);
-                        us += __ldcg(partials + ((size_t)sp * M + m) * N + row0 + r + 8);
-                    }
-                    out[(size_t)m * (N >> 1) + (row0 >> 1) + r] = gate(gs, us);
                 }
             }
             if (tid == 0) tickets[blockIdx.x] = 0;
@@ -507,9 +571,10 @@ static bool encode_plane_map(CUtensorMap* map, const void* qweight, long long pl
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int W, int OCC, int MODE, bool GATED = false>
+template <int W, int OCC, int MODE, bool DEC = false>
 static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const uint16_t* lut, __half* out, int M, int N,
-                                  int K, int splits, int split_chunks, float* partials, int* tickets, cudaStream_t stream) {
+                                  int K, int splits, int split_chunks, float* partials, int* tickets, cudaStream_t stream,
+                                  const GemvEpilogue& epi) {
     using T = GemvTmaCfg<W, OCC, MODE>;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -518,7 +583,7 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         int most = 0;
         for (int mp = 1; mp <= 8; mp *= 2) most = T::total(mp) > most ? T::total(mp) : most;
-        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
@@ -533,16 +598,17 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, GATED>, map, x, lut, out, M, N, K, mpad, split_chunks,
-                              partials, tickets);
+    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC>, map, x, lut, out, M, N, K, mpad, split_chunks,
+                              partials, tickets, epi);
 }
 
 template <int W>
 static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plane_stride, const uint16_t* lut, __half* out,
                               int M, int N, int K, int splits, float* partials, int* tickets, cudaStream_t stream,
-                              bool* used, int gated = 0) {
+                              bool* used, const GemvEpilogue* epi = nullptr) {
     *used = false;
-    if (gated && M > 8) return cudaSuccess;                  // the gated epilogue is for decode batches
+    if (epi && M > 8) return cudaSuccess;                    // the decoder's epilogues are for decode batches
+    const GemvEpilogue plain = {};
     CUtensorMap map;
     if (!make_plane_map(&map, q, plane_stride, N, K, W)) return cudaSuccess;      // caller falls back to cp.async
     const int chunks = (K + 1023) / 1024;
@@ -562,8 +628,8 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
     if (M > 8 && splits > 1) { *used = false; return cudaSuccess; }              // the caller runs the passes one by one
     const bool many_blocks = (long long)(N / 16) * splits * ((M + 7) / 8) >= 3LL * sms;
 #define AP_TMA_GO(OCC_, MODE_) \
-    return gated ? launch_tma_occ<W, OCC_, MODE_, true>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream) \
-                 : launch_tma_occ<W, OCC_, MODE_, false>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream)
+    return epi ? launch_tma_occ<W, OCC_, MODE_, true>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi) \
+               : launch_tma_occ<W, OCC_, MODE_, false>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, plain)
     if constexpr (W == 3) {
         if (many_blocks) AP_TMA_GO(3, 2);
         AP_TMA_GO(2, 2);

@@ -1,9 +1,26 @@
 // Internal launch interface between the C-ABI translation unit and the kernels.
 #pragma once
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 namespace ap {
+
+// What the decode kernel's decoder variants do with a finished tile (see the epilogue of
+// gemv_kbit_tma_kernel): mode 1 gated (silu(gate) * up of stacked rows), 2 scaled by the per-row
+// rsqrt(mean square + eps) taken from `ssq_in` ([M][ssq_blocks] partial sums of squares, mean over
+// 1 / inv_width values), 3 both, 4 residual update (`resid` [M][N] += product; out = new residual *
+// `norm_w`; `ssq_out` [M][N / 16] partial sums of squares of the new residual).
+struct GemvEpilogue {
+    int mode;
+    const float* ssq_in;
+    int ssq_blocks;
+    float inv_width;
+    float eps;
+    __half* resid;
+    const __half* norm_w;
+    float* ssq_out;
+};
 
 // All launchers enqueue on `stream`, never synchronise, never allocate, and return the
 // launch status from cudaGetLastError().
@@ -13,12 +30,11 @@ cudaError_t launch_dequant(const void* qweight, long long plane_stride, const vo
 // `splits` > 1 cuts K into that many ranges handled by different CTAs (fast kernel only); it needs
 // `partials` (splits*M*N floats, any contents) and `tickets` (N/16 ints, zero on entry, zero again
 // on completion).  With splits <= 1 or null scratch pointers every CTA takes a whole row range.
-// `gated` != 0: the rows are a gated MLP's gate and up projections stacked tile by tile (eight gate rows, then
-// the eight up rows of the same features, per 16 rows) and `out` is [M][N/2] = silu(gate) * up; only the fast
-// kernel has that epilogue (cudaErrorNotSupported otherwise; M <= 8).
+// `epi` non-null: one of the decoder's epilogues (modes 1 and 3: `out` is [M][N/2]); only the fast kernel has
+// them (cudaErrorNotSupported otherwise; M <= 8).
 cudaError_t launch_gemv(const void* x, const void* qweight, long long plane_stride, const void* lut, void* out,
                         int M, int N, int K, int w_bits, int splits, float* partials, int* tickets,
-                        cudaStream_t stream, int gated = 0);
+                        cudaStream_t stream, const GemvEpilogue* epi = nullptr);
 bool gemv_fast_path(const void* x, const void* qweight, long long plane_stride, const void* lut, int N, int K);
 // Reads (after synchronising the device) and clears the flag that a decode kernel sets when one of its
 // bounded waits ran out.

@@ -53,12 +53,8 @@ def main():
 
     real = model.lib
     timed(f"w_bits {w}: whole step")
-    model.lib = Without(real, {"ap_decode_attention"})
-    timed("without attention")
-    model.lib = Without(real, {"ap_decode_attention", "ap_rope_cache"})
-    timed("without attention and RoPE/cache write")
-    model.lib = Without(real, {"ap_decode_attention", "ap_rope_cache", "ap_add_rmsnorm"})
-    timed("without any of the small kernels (linears with SiLU * up in the gate+up launch, lm_head and embedding left)")
+    model.lib = Without(real, {"ap_decode_attention_rope"})
+    timed("without attention (with rotary embedding and cache write inside)")
     model.lib = real
     forward = AnyPrecisionLinear.forward
     outs = {}
@@ -69,13 +65,22 @@ def main():
             outs[key] = torch.zeros(key, dtype=torch.float16, device=x.device)
         return outs[key]
 
-    def no_gated(self, x, out=None, **kwargs):
-        return out if out is not None else no_linear(self, x)[:, :self.out_features // 2]
+    def no_fused(self, x, *args, out=None, **kwargs):
+        if out is not None:
+            return out
+        full = no_linear(self, x)
+        return full[:, :self.out_features // 2] if getattr(self, "gated", False) else full
 
-    forward_gated = AnyPrecisionLinear.forward_gated
-    AnyPrecisionLinear.forward, AnyPrecisionLinear.forward_gated = no_linear, no_gated
-    timed("without the linears (small kernels, lm_head and embedding left)")
-    AnyPrecisionLinear.forward, AnyPrecisionLinear.forward_gated = forward, forward_gated
+    saved = {name: getattr(AnyPrecisionLinear, name) for name in ("forward_gated", "forward_prenorm", "forward_residual")}
+    AnyPrecisionLinear.forward = no_linear
+    for name in saved:
+        setattr(AnyPrecisionLinear, name, no_fused)
+    timed("without the linears (attention, first norm, lm_head and embedding left)")
+    AnyPrecisionLinear.forward = forward
+    for name, fn in saved.items():
+        setattr(AnyPrecisionLinear, name, fn)
+    model.fold_norms = False
+    timed("whole step with every norm a launch of its own (fold_norms = False)")
 
 
 if __name__ == "__main__":

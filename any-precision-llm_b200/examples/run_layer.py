@@ -5,7 +5,8 @@
 `--reps` distinct random layers are created (uniform parent codes drawn as random bitplanes, sorted
 N(0, 0.02) fp16 tables) and the chosen operator is called once on each:
 `matmul` = any_precision_ext.matmul_kbit (decode GEMV), `gemm` = gemm_kbit (fused prefill),
-`dequant` = dequant_kbit.  Prints the mean |y| of the last result so the work cannot be elided.
+`dequant` = dequant_kbit, `quantize` = quantize.seed_and_upscale_layer (seed 3 bits, parent 8; random fp16-valued
+weights and squared-normal sensitivities instead of packed operands).  Prints the mean |y| of the last result so the work cannot be elided.
 """
 import argparse
 import os
@@ -21,7 +22,7 @@ from anyprec_b200 import packing
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["matmul", "gemm", "dequant"], default="matmul")
+    ap.add_argument("--op", choices=["matmul", "gemm", "dequant", "quantize"], default="matmul")
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--w", type=int, default=4)
@@ -30,6 +31,16 @@ def main():
     a = ap.parse_args()
     torch.cuda.set_device(0)
     gen = torch.Generator(device="cuda").manual_seed(0)
+    if a.op == "quantize":
+        from anyprec_b200 import quantize
+        codes = None
+        for _ in range(a.reps):
+            w = (torch.randn((a.N, a.K), device="cuda", generator=gen) * 0.02).half().float()
+            s = torch.randn((a.N, a.K), device="cuda", generator=gen) ** 2
+            luts, codes = quantize.seed_and_upscale_layer(w, s)
+        torch.cuda.synchronize()
+        print("done", float(codes.float().mean()))
+        return
     qs = [packing.random_qweight(8, a.N, a.K, device="cuda", generator=gen) for _ in range(a.reps)]
     luts = [packing.random_lut(a.N, a.w, device="cuda", generator=gen) for _ in range(a.reps)]
     x = torch.randn((a.M, a.K), device="cuda", generator=gen).half()

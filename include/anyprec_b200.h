@@ -114,6 +114,27 @@ int ap_matmul_kbit_gated(const void* x, const void* qweight, int64_t plane_strid
                          void* stream);
 
 /*
+ * The decode product with a pre-norm decoder's residual add and RMSNorm folded into it (no counterpart in the
+ * reference, which runs the stock Hugging Face decoder layer around its linears).  A pair of calls replaces
+ * "h += linear_1(...); y = rmsnorm(h) * g; z = linear_2(y)":
+ *   ap_matmul_kbit_residual  p = x W^T as ap_matmul_kbit_splitk computes it; resid[M][N] (fp16) += fp16(p) in place;
+ *                            out[M][N] = fp16(new resid * norm_weight[N]) (NOT yet divided by the root mean square);
+ *                            ssq_out[M][N / 16] (fp32) = per 16-row tile the sum of squares of the new resid.
+ *   ap_matmul_kbit_prenorm   out = fp16(r_m * (x W^T)) with r_m = rsqrt(sum(ssq[m][0 .. ssq_blocks)) / width + eps):
+ *                            x is the `out` of ap_matmul_kbit_residual, ssq its ssq_out, width its N; a product
+ *                            commutes with a scale per batch row, so this is linear_2(rmsnorm(h) * g) up to fp16
+ *                            rounding of x.  gated != 0: additionally the epilogue of ap_matmul_kbit_gated
+ *                            (operand stacked tile by tile, out[M][N / 2]), the scale applied before the activation.
+ * Same limits as ap_matmul_kbit_gated (M <= 8, N % 16 == 0, fast-kernel operands), AP_ERR_UNSUPPORTED otherwise.
+ */
+int ap_matmul_kbit_prenorm(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out,
+                           int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
+                           int gated, const void* ssq, int ssq_blocks, int width, float eps, void* stream);
+int ap_matmul_kbit_residual(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out,
+                            int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
+                            void* resid, const void* norm_weight, void* ssq_out, void* stream);
+
+/*
  * ap_matmul_kbit_splitk for callers that have no way to provide a workspace: code that runs where
  * device allocation is off limits (inside a serving loop with a frozen memory pool, under a
  * framework that owns every byte of device memory, in a plugin that is handed only its inputs and
@@ -237,6 +258,12 @@ int ap_unpack_codes(const void* qweight, int64_t plane_stride, void* codes, int 
  *                   heads); it needs `scratch`: 16-byte aligned device memory of
  *                   ap_decode_attention_scratch_bytes(...) bytes whose first sequences * heads ints are ticket
  *                   counters, ZERO before the first call and left zero by every call
+ *   ap_decode_attention_rope  ap_rope_cache (rows_per_seq = 1) and ap_decode_attention in one launch: the rows of
+ *                   qkv are the RAW q | k | v of the new token (q_row_stride >= (heads + 2 kv_heads) * head_dim, a
+ *                   multiple of 8; head_dim a multiple of 16), the caches hold the earlier positions; q and k are
+ *                   rotated on the fly, the rotated k and v of position pos[b] are stored in the caches (qkv itself
+ *                   is left as it was), and the result equals the two separate calls bit for bit.  A position
+ *                   outside [0, max_seq) rotates and stores nothing, as in ap_rope_cache.
  */
 int ap_add_rmsnorm(void* h, const void* delta, const void* weight, void* y, int rows, int hidden, float eps,
                    void* stream);
@@ -247,6 +274,9 @@ size_t ap_decode_attention_scratch_bytes(int sequences, int heads, int head_dim,
 int ap_decode_attention(const void* qkv, int q_row_stride, const void* k_cache, const void* v_cache, const void* pos,
                         void* out, int sequences, int heads, int kv_heads, int head_dim, int max_seq, float scale,
                         int splits, void* scratch, void* stream);
+int ap_decode_attention_rope(const void* qkv, int q_row_stride, const void* cos_sin, void* k_cache, void* v_cache,
+                             const void* pos, void* out, int sequences, int heads, int kv_heads, int head_dim, int max_seq,
+                             float scale, int splits, void* scratch, void* stream);
 
 /*
  * Seed + incremental-upscale quantisation of a weight matrix, one thread block per row.  Replaces the

@@ -84,12 +84,17 @@ def reference_forward(sd, config, ids, w):
     return norm(h, sd["model.norm.weight"]) @ sd["lm_head.weight"].float().T
 
 
+@pytest.mark.parametrize("fold", [True, False])
 @pytest.mark.parametrize("batch", [1, 2])
-def test_decoder_prefill_and_decode_against_fp32_forward(batch):
+def test_decoder_prefill_and_decode_against_fp32_forward(batch, fold):
+    """`fold`: the decode step with every residual add + RMSNorm folded into the products around it (five
+    launches per layer), or with the norms as launches of their own."""
     from anyprec_b200 import checkpoint
     from anyprec_b200.decoder import AnyPrecisionLlama
     config, sd = checkpoint.read_packed(CKPT)
     model = AnyPrecisionLlama.from_packed(CKPT, device="cuda", batch=batch, max_seq=64 if batch == 1 else 192)
+    model.fold_norms = fold
+    assert model._folded_norms()
     assert model.precisions == [3, 4, 5] and model.spec.kv_heads == 2
     gen = torch.Generator().manual_seed(batch)
     ids = torch.randint(0, config["vocab_size"], (batch, 20), generator=gen)
@@ -107,7 +112,7 @@ def test_decoder_prefill_and_decode_against_fp32_forward(batch):
             for b in range(batch):
                 seqs[b].append(toks[b])
             model._decode_step()
-            y = (model.y.float() @ model.lm_head.float().T).cpu()
+            y = model.last_logits().cpu()
             for b in range(batch):
                 ref = reference_forward(sd, config, seqs[b], w)
                 close(y[b].numpy(), ref[-1].numpy(), max_rel=3e-2, mean_abs=5e-3)
@@ -122,6 +127,11 @@ def test_generate_graph_replay_equals_eager_and_restores_precision():
     model.set_precision(4)
     for w in (3, 5):
         eager = model.generate(ids, 24, precision=w, use_graph=False)
+        model.fold_norms = False                                               # the unfolded step picks the same tokens
+        model._graphs.clear()
+        assert torch.equal(model.generate(ids, 24, precision=w, use_graph=True), eager)
+        model.fold_norms = True
+        model._graphs.clear()
         graph = model.generate(ids, 24, precision=w, use_graph=True)
         again = model.generate(ids, 24, precision=w, use_graph=True)          # second call replays the cached graph
         assert eager.shape == (1, 36) and torch.equal(eager[:, :12].cpu(), ids)
@@ -145,3 +155,53 @@ def test_random_init_llama_shapes_run():
         assert out.shape == (2, 56) and int(out.max()) < spec.vocab
     import any_precision_ext as ext
     assert not ext.take_wait_expired()
+
+
+@pytest.mark.parametrize("heads,kv_heads,D,splits", [(8, 8, 128, 1), (8, 2, 128, 4), (4, 1, 64, 3), (2, 2, 32, 2), (2, 1, 256, 5)])
+def test_attention_with_rotation_inside_equals_the_two_separate_kernels(heads, kv_heads, D, splits):
+    """ap_decode_attention_rope against ap_rope_cache followed by ap_decode_attention: outputs and both caches
+    bit for bit, at positions that put the new token first, inside and at the end of a split, and out of range."""
+    from anyprec_b200.decoder import _ops
+    lib = _ops()
+    B, max_seq = 3, 300
+    g = torch.Generator(device="cuda").manual_seed(heads * 100 + D)
+    width = (heads + 2 * kv_heads) * D
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+    ang = torch.arange(max_seq, dtype=torch.float64)[:, None] * inv[None, :]
+    cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).float().cuda().contiguous()
+    scratch_bytes = lib.ap_decode_attention_scratch_bytes(B, heads, D, splits)
+    stream = torch.cuda.current_stream().cuda_stream
+    for positions in ([0, 1, 2], [255, 256, 299], [17, 128, 64], [300, -1, 5]):
+        pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
+        qkv = torch.randn((B, width), device="cuda", generator=g).half()
+        k0 = torch.randn((B, kv_heads, max_seq, D), device="cuda", generator=g).half()
+        v0 = torch.randn((B, kv_heads, max_seq, D), device="cuda", generator=g).half()
+        results = []
+        for fused in (False, True):
+            q, k, v = qkv.clone(), k0.clone(), v0.clone()
+            out = torch.zeros((B, heads * D), dtype=torch.float16, device="cuda")
+            scratch = torch.zeros(max(scratch_bytes, 16), dtype=torch.uint8, device="cuda")
+            sp = scratch.data_ptr() if splits > 1 else None
+            if fused:
+                rc = lib.ap_decode_attention_rope(q.data_ptr(), width, cos_sin.data_ptr(), k.data_ptr(), v.data_ptr(), pos.data_ptr(),
+                                                  out.data_ptr(), B, heads, kv_heads, D, max_seq, D ** -0.5, splits, sp, stream)
+                assert rc == 0 and torch.equal(q, qkv)                  # the raw row is left alone
+            else:
+                assert lib.ap_rope_cache(q.data_ptr(), cos_sin.data_ptr(), pos.data_ptr(), k.data_ptr(), v.data_ptr(), B, 1, heads,
+                                         kv_heads, D, max_seq, stream) == 0
+                assert lib.ap_decode_attention(q.data_ptr(), width, k.data_ptr(), v.data_ptr(), pos.data_ptr(), out.data_ptr(), B,
+                                               heads, kv_heads, D, max_seq, D ** -0.5, splits, sp, stream) == 0
+            torch.cuda.synchronize()
+            assert int(scratch[: B * heads * 4].view(torch.int32).abs().sum()) == 0 or splits == 1
+            results.append((out, k, v))
+        (o1, k1, v1), (o2, k2, v2) = results
+        valid = [b for b, p in enumerate(positions) if 0 <= p < max_seq]
+        assert torch.equal(k1, k2) and torch.equal(v1, v2), positions
+        assert torch.equal(o1[valid], o2[valid]), positions
+        # and the caches did change exactly at the new positions
+        for b, p in enumerate(positions):
+            if 0 <= p < max_seq:
+                assert not torch.equal(k2[b, :, p], k0[b, :, p]) and torch.equal(v2[b, :, p], qkv[b, (heads + kv_heads) * D:].view(kv_heads, D))
+        for b, p in enumerate(positions):                   # the earlier positions are untouched
+            q0 = min(max(p, 0), max_seq)
+            assert torch.equal(k2[b, :, :q0], k0[b, :, :q0]) and torch.equal(v2[b, :, :q0], v0[b, :, :q0])

@@ -108,3 +108,57 @@ def test_gated_refuses_what_the_kernel_does_not_take():
     assert not ext.gated_supported(x, q, luts[4])
     with pytest.raises(ValueError):
         ext.matmul_kbit(x, q, luts[4], 4, gated=True)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_residual_and_prenorm_products_fold_add_and_rmsnorm(M, splits):
+    """h += linear_1(x); z = linear_2(rmsnorm(h) * g) as two launches (ap_matmul_kbit_residual,
+    ap_matmul_kbit_prenorm) against the same chain with the add and the norm written out."""
+    import any_precision_ext as ext
+    H, K1, F = 256, 1024, 192
+    c1, l1 = make_layer(H, K1, seed=41)
+    c2, l2 = make_layer(F, H, seed=42)
+    q1, q2 = dev(oracle.pack(c1)), dev(oracle.pack(c2))
+    rng = np.random.default_rng(M + splits)
+    x = dev(rng.normal(size=(M, K1)).astype(np.float16))
+    h0 = dev(rng.normal(size=(M, H)).astype(np.float16))
+    g = dev((1.0 + 0.1 * rng.normal(size=H)).astype(np.float16))
+    eps = 1e-5
+    for w in (3, 4, 6, 8):
+        t1, t2 = dev(l1[w]), dev(l2[w])
+        # written out
+        p = ext.matmul_kbit(x, q1, t1, w, splits=splits)
+        h_ref = (h0.float() + p.float()).half()
+        r = torch.rsqrt(h_ref.float().pow(2).mean(-1, keepdim=True) + eps)
+        y_ref = ((h_ref.float() * r).half().float() * g.float()).half()
+        z_ref = ext.matmul_kbit(y_ref, q2, t2, w).float()
+        # folded
+        h = h0.clone()
+        ssq = torch.full((M, H // 16), float("nan"), dtype=torch.float32, device="cuda")
+        y = ext.matmul_kbit(x, q1, t1, w, splits=splits, residual=(h, g, ssq))
+        assert torch.equal(h, h_ref)                                   # the residual stream itself: bit for bit
+        assert torch.equal(y, (h_ref.float() * g.float()).half())
+        assert torch.allclose(ssq.sum(-1), h_ref.float().pow(2).sum(-1), rtol=1e-5)
+        z = ext.matmul_kbit(y, q2, t2, w, prenorm=(ssq, H, eps)).float()
+        err = (z - z_ref).abs()
+        assert float((err / z_ref.abs().clamp_min(0.05 * float(z_ref.abs().max()))).max()) < 1e-2, w
+        assert float(err.mean()) < 1e-3 * max(1.0, float(z_ref.abs().max()))
+
+
+def test_gated_prenorm_product():
+    import any_precision_ext as ext
+    F, K = 128, 512
+    gate, up, q, luts = build(F, K, seed=77)
+    rng = np.random.default_rng(3)
+    M = 4
+    hsrc = dev(rng.normal(size=(M, K)).astype(np.float16))                 # plays h * g
+    ssq = torch.zeros((M, K // 16), dtype=torch.float32, device="cuda")
+    ssq[:, 0] = torch.tensor([K * 4.0, K * 0.25, K * 1.0, K * 9.0])         # root mean squares 2, 0.5, 1, 3
+    r = torch.tensor([0.5, 2.0, 1.0, 1.0 / 3.0], device="cuda")[:, None]
+    for w in (3, 5, 8):
+        y = ext.matmul_kbit(hsrc, q, luts[w], w, gated=True, prenorm=(ssq, K, 0.0)).float()
+        plain = ext.matmul_kbit(hsrc, q, luts[w], w).float().view(M, F // 8, 2, 8)
+        gs, us = (plain[:, :, 0] * r[:, :, None]).half().float(), (plain[:, :, 1] * r[:, :, None]).half().float()
+        ref = (torch.nn.functional.silu(gs).half().float() * us).half().float().reshape(M, F)
+        assert torch.allclose(y, ref, rtol=4e-3, atol=1e-4), w
