@@ -273,7 +273,8 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
     pre-norm decoder's residual add and RMSNorm into a pair of products: the first adds its result to
     ``h`` in place, returns ``h * norm_weight`` and leaves per-tile sums of squares in ``ssq`` (fp32
     ``[rows, N / 16]``); the second takes that as ``x`` and scales its result by
-    ``rsqrt(sum(ssq) / width + eps)`` (``ap_matmul_kbit_residual`` / ``ap_matmul_kbit_prenorm``).
+    ``rsqrt(sum(ssq) / width + eps)`` (``ap_matmul_kbit_residual`` / ``ap_matmul_kbit_prenorm``; a
+    fourth entry of ``prenorm`` gives the number of partial sums per row when another kernel wrote them).
     """
     N, K, plane_stride = _check_operands(qweight, lut, w_bits)
     if x.dtype != torch.float16:
@@ -315,11 +316,12 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
             rc = lib.ap_matmul_kbit_residual(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),
                                              M, N, K, w_bits, nsp, wsp, wsn, h.data_ptr(), norm_w.data_ptr(), ssq.data_ptr(), stream)
         elif prenorm is not None:
-            ssq, width, eps = prenorm
-            if ssq.dtype != torch.float32 or width % 16 or ssq.numel() < M * (width // 16):
-                raise ValueError("prenorm=(ssq fp32 [rows * width / 16], width, eps)")
+            ssq, width, eps = prenorm[:3]
+            blocks = prenorm[3] if len(prenorm) > 3 else width // 16       # entries per row: one per 16-row tile of the writer
+            if ssq.dtype != torch.float32 or blocks < 1 or ssq.numel() < M * blocks:
+                raise ValueError("prenorm=(ssq fp32 [rows * blocks], width, eps[, blocks = width / 16])")
             rc = lib.ap_matmul_kbit_prenorm(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),
-                                            M, N, K, w_bits, nsp, wsp, wsn, 1 if gated else 0, ssq.data_ptr(), width // 16,
+                                            M, N, K, w_bits, nsp, wsp, wsn, 1 if gated else 0, ssq.data_ptr(), blocks,
                                             width, eps, stream)
         elif gated:
             rc = lib.ap_matmul_kbit_gated(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), out.data_ptr(),

@@ -37,6 +37,10 @@ def _lib():
     lib.ap_comm_last_error.restype = ctypes.c_char_p
     lib.ap_allreduce_oneshot.restype = i
     lib.ap_allreduce_oneshot.argtypes = [vp, vp, i, ctypes.POINTER(vp), i, i, sz, vp, vp]
+    lib.ap_allreduce_residual_blocks.restype = i
+    lib.ap_allreduce_residual_blocks.argtypes = [i, i]
+    lib.ap_allreduce_oneshot_residual.restype = i
+    lib.ap_allreduce_oneshot_residual.argtypes = [vp, vp, i, i, vp, vp, vp, ctypes.POINTER(vp), i, i, sz, vp, vp]
     lib._comm_ready = True
     return lib
 
@@ -102,6 +106,32 @@ class OneShotAllReduce:
                                                self.rank, self.world, self.max_payload, self.status.data_ptr(),
                                                torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "ap_allreduce_oneshot")
+        return out
+
+    def residual_blocks(self, rows: int, row_len: int) -> int:
+        """Entries per row that ``residual`` leaves in ``ssq`` (0: shape not supported)."""
+        return self.lib.ap_allreduce_residual_blocks(rows, row_len)
+
+    def residual(self, tensor: torch.Tensor, h: torch.Tensor, norm_weight: torch.Tensor, ssq: torch.Tensor,
+                 out: torch.Tensor) -> torch.Tensor:
+        """The sum of ``tensor [rows, N]`` over the ranks, added to the residual stream ``h [rows, N]`` in place;
+        ``out = h * norm_weight`` (not yet normalised) and ``ssq[rows, residual_blocks(rows, N)]`` the partial sums
+        of squares of the new ``h``: the first half of a folded residual add + RMSNorm across a row-parallel
+        layer (``ap_allreduce_oneshot_residual``; the second half is ``matmul_kbit(prenorm=)``)."""
+        for t in (tensor, h, out, norm_weight):
+            if t.dtype != torch.float16 or not t.is_contiguous() or t.device != self.device:
+                raise TypeError("OneShotAllReduce.residual needs contiguous float16 tensors on the buffers' device")
+        rows, n = tensor.shape
+        blocks = self.residual_blocks(rows, n)
+        if h.shape != tensor.shape or out.shape != tensor.shape or norm_weight.numel() != n or blocks == 0 or \
+                ssq.dtype != torch.float32 or ssq.numel() < rows * blocks or ssq.device != self.device:
+            raise ValueError("residual: h and out as tensor, norm_weight [N], ssq fp32 with rows * residual_blocks entries")
+        with torch.cuda.device(self.device):
+            rc = self.lib.ap_allreduce_oneshot_residual(tensor.data_ptr(), out.data_ptr(), rows, n, h.data_ptr(),
+                                                        norm_weight.data_ptr(), ssq.data_ptr(), self._table, self.rank, self.world,
+                                                        self.max_payload, self.status.data_ptr(),
+                                                        torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "ap_allreduce_oneshot_residual")
         return out
 
     def wait_expired(self) -> bool:

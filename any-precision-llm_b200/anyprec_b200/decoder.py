@@ -370,11 +370,14 @@ class AnyPrecisionLlama:
             "ap_decode_attention_rope")
 
     def _folded_norms(self):
-        """Whether a decode step can fold every residual add + RMSNorm into the products around it: one GPU
-        (a row-parallel output must be summed over the ranks before it is added), at most eight sequences,
-        shapes the decode kernel takes."""
-        if self.tp_world != 1 or self.batch > 8:
+        """Whether a decode step can fold every residual add + RMSNorm into the launches around it (on one GPU
+        into the products' epilogues; across tensor-parallel ranks the add goes into the one-shot all-reduce
+        that sums a row-parallel output): at most eight sequences, shapes the decode kernel takes."""
+        if self.batch > 8:
             return False
+        if self.tp_world > 1 and (self.allreduce is None or not hasattr(self.allreduce, "residual") or
+                                  self.allreduce.residual_blocks(self.batch, self.spec.hidden) == 0):
+            return False                                   # the process group's all-reduce has no folded form
         return all(m.bias is None and m.in_features % 128 == 0 and m.out_features % 16 == 0
                    for L in self.layers for m in (L.qkv, L.o, L.gate_up, L.down))
 
@@ -386,15 +389,24 @@ class AnyPrecisionLlama:
         sequence, so the arg-max needs none."""
         s = self.spec
         h, y, ssq = self.h, self.y, self.ssq
+        tp = self.tp_world > 1
+        blocks = self.allreduce.residual_blocks(self.batch, s.hidden) if tp else None   # partial sums per row in ssq
+
+        def add_and_scale(layer, x, norm_weight):
+            if tp:                                           # this rank's partial product, summed and added by the all-reduce
+                self.allreduce.residual(layer(x), h, norm_weight, ssq, out=y)
+            else:
+                layer.forward_residual(x, h, norm_weight, ssq, out=y)
+
         h.copy_(self.embed[self.tok])
         self._add_rmsnorm(h, None, self.layers[0].in_norm, y)
         for li, L in enumerate(self.layers):
-            qkv = L.qkv(y) if li == 0 else L.qkv.forward_prenorm(y, ssq, s.hidden, s.rms_eps)
+            qkv = L.qkv(y) if li == 0 else L.qkv.forward_prenorm(y, ssq, s.hidden, s.rms_eps, blocks=blocks)
             self._attention(L, qkv)
-            L.o.forward_residual(self.attn, h, L.post_norm, ssq, out=y)
-            L.gate_up.forward_prenorm(y, ssq, s.hidden, s.rms_eps, out=self.act)
+            add_and_scale(L.o, self.attn, L.post_norm)
+            L.gate_up.forward_prenorm(y, ssq, s.hidden, s.rms_eps, out=self.act, blocks=blocks)
             nxt = self.layers[li + 1].in_norm if li + 1 < len(self.layers) else self.final_norm
-            L.down.forward_residual(self.act, h, nxt, ssq, out=y)
+            add_and_scale(L.down, self.act, nxt)
         logits = y @ self.lm_head.T
         self.tok.copy_(logits.argmax(dim=-1))
         self.pos.add_(1)

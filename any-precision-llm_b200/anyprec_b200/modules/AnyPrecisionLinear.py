@@ -203,13 +203,13 @@ class AnyPrecisionLinear(nn.Module):
         w_bits, lut = self._decode_operands(x, kwargs)
         return _ext.matmul_kbit(x, self.qweight, lut, w_bits, out=out, residual=(h, norm_weight, ssq))
 
-    def forward_prenorm(self, x, ssq, width, eps, out=None, **kwargs):
+    def forward_prenorm(self, x, ssq, width, eps, out=None, blocks=None, **kwargs):
         """``self(rmsnorm-scaled x)`` for the ``x`` and ``ssq`` that ``forward_residual`` of the previous layer
         left (``width`` = that layer's ``out_features``); with a ``fuse_gated`` module the result is
         ``silu(gate) * up``."""
         w_bits, lut = self._decode_operands(x, kwargs)
         return _ext.matmul_kbit(x, self.qweight, lut, w_bits, out=out, gated=getattr(self, 'gated', False),
-                                prenorm=(ssq, width, eps))
+                                prenorm=(ssq, width, eps) if blocks is None else (ssq, width, eps, blocks))
 
     def forward_split(self, x, **kwargs):
         """``forward`` of a fused module, cut back into the original layers' outputs (views)."""

@@ -77,9 +77,16 @@ __device__ __forceinline__ uint32_t f2h(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// RES: the sum is a row-parallel layer's output that a pre-norm decoder adds to its residual stream and
+// normalises next.  The grid is (rows x blocks per row), a block's range lies inside one row of `row_vec`
+// vectors, and step 4 becomes resid += fp16(sum) in place, out = new resid * norm_w (not yet divided by the root
+// mean square), ssq_out[row][block of the row] = sum of squares of the new resid in the block's range: what
+// ap_matmul_kbit_prenorm takes.  All ranks compute the same bits, so the replicated residual streams stay equal.
+template <bool RES>
 __global__ void __launch_bounds__(kThreads)
 allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* __restrict__ out, int n_vec, int rank,
-                         int world, size_t cap, int* __restrict__ status) {
+                         int world, size_t cap, int* __restrict__ status, int row_vec, int blocks_per_row,
+                         uint4* __restrict__ resid, const uint4* __restrict__ norm_w, float* __restrict__ ssq_out) {
     unsigned char* mine = peers.buf[rank];
     uint32_t* header = reinterpret_cast<uint32_t*>(mine);      // [0] calls, [1] blocks done, [2] error
     __shared__ uint32_t s_seq;
@@ -100,9 +107,18 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
     const int gen = seq & 1u;
 
     // this block's contiguous share of the vector
-    const int per_block = (n_vec + gridDim.x - 1) / gridDim.x;
-    const int v0 = blockIdx.x * per_block;
-    const int v1 = (v0 + per_block < n_vec) ? (v0 + per_block) : n_vec;
+    int v0, v1, row_base = 0;
+    if constexpr (RES) {
+        const int m = blockIdx.x / blocks_per_row, j = blockIdx.x % blocks_per_row;
+        const int per = (row_vec + blocks_per_row - 1) / blocks_per_row;
+        row_base = m * row_vec;
+        v0 = row_base + (j * per < row_vec ? j * per : row_vec);
+        v1 = row_base + ((j + 1) * per < row_vec ? (j + 1) * per : row_vec);
+    } else {
+        const int per_block = (n_vec + gridDim.x - 1) / gridDim.x;
+        v0 = blockIdx.x * per_block;
+        v1 = (v0 + per_block < n_vec) ? (v0 + per_block) : n_vec;
+    }
 
     // 1. push
     for (int v = v0 + threadIdx.x; v < v1; v += kThreads) {
@@ -145,6 +161,7 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
         return;
     }
     // 4. reduce in rank order
+    float sq = 0.f;
     for (int v = v0 + threadIdx.x; v < v1; v += kThreads) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int p = 0; p < world; p++) {
@@ -158,7 +175,38 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
         r.y = f2h(acc[2], acc[3]);
         r.z = f2h(acc[4], acc[5]);
         r.w = f2h(acc[6], acc[7]);
-        out[v] = r;
+        if constexpr (RES) {
+            const uint4 hv = resid[v], wv = norm_w[v - row_base];
+            uint4 hn, y;
+            auto one = [&](uint32_t sum2, uint32_t h2, uint32_t w2, uint32_t& hn2, uint32_t& y2) {
+                const float2 o = h2f(sum2), hf = h2f(h2), wf = h2f(w2);
+                hn2 = f2h(hf.x + o.x, hf.y + o.y);
+                const float2 n = h2f(hn2);
+                y2 = f2h(n.x * wf.x, n.y * wf.y);
+                sq += n.x * n.x + n.y * n.y;
+            };
+            one(r.x, hv.x, wv.x, hn.x, y.x);
+            one(r.y, hv.y, wv.y, hn.y, y.y);
+            one(r.z, hv.z, wv.z, hn.z, y.z);
+            one(r.w, hv.w, wv.w, hn.w, y.w);
+            resid[v] = hn;
+            out[v] = y;
+        } else {
+            out[v] = r;
+        }
+    }
+    if constexpr (RES) {
+        // the block's sum of squares in a fixed order: shuffle tree, then the warps' sums left to right
+        __shared__ float s_sq[kThreads / 32];
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o2);
+        if ((threadIdx.x & 31) == 0) s_sq[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+            for (int w2 = 0; w2 < kThreads / 32; w2++) t += s_sq[w2];
+            ssq_out[blockIdx.x] = t;
+        }
     }
     finish();
 }
@@ -217,8 +265,11 @@ extern "C" int ap_comm_close(void* ptr) {
 
 extern "C" const char* ap_comm_last_error(void) { return g_comm_err; }
 
-extern "C" int ap_allreduce_oneshot(const void* src, void* out, int count, void* const* peer_buffers, int rank, int world,
-                                    size_t max_payload_bytes, int* status, void* stream) {
+namespace {
+
+int allreduce_impl(const void* src, void* out, int count, void* const* peer_buffers, int rank, int world,
+                   size_t max_payload_bytes, int* status, void* stream, int rows, void* resid, const void* norm_weight,
+                   void* ssq_out) {
     if (!src || !out || !peer_buffers) return AP_ERR_NULL_POINTER;
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || count < 8 || count % 8) return AP_ERR_BAD_SHAPE;
     const size_t cap = (max_payload_bytes + 255) & ~static_cast<size_t>(255);
@@ -233,6 +284,18 @@ extern "C" int ap_allreduce_oneshot(const void* src, void* out, int count, void*
     // the same grid on every rank for a given count: blocks of different ranks pair up by index
     int blocks = (n_vec + 2 * kThreads - 1) / (2 * kThreads);
     blocks = blocks < 1 ? 1 : (blocks > kMaxBlocks ? kMaxBlocks : blocks);
+    int row_vec = 0, bpr = 0;
+    if (resid) {
+        if (!norm_weight || !ssq_out) return AP_ERR_NULL_POINTER;
+        if (rows < 1 || count % rows || (count / rows) % 8) return AP_ERR_BAD_SHAPE;
+        if ((reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(norm_weight)) & 15 ||
+            reinterpret_cast<uintptr_t>(ssq_out) & 3)
+            return AP_ERR_BAD_ALIGNMENT;
+        row_vec = count / rows / 8;
+        bpr = ap_allreduce_residual_blocks(rows, count / rows);
+        if (bpr < 1) return AP_ERR_UNSUPPORTED;
+        blocks = rows * bpr;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks);
     cfg.blockDim = dim3(kThreads);
@@ -242,7 +305,36 @@ extern "C" int ap_allreduce_oneshot(const void* src, void* out, int count, void*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel, t, static_cast<const uint4*>(src),
-                                       static_cast<uint4*>(out), n_vec, rank, world, cap, status);
+    cudaError_t e = resid ? cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<true>, t, static_cast<const uint4*>(src),
+                                               static_cast<uint4*>(out), n_vec, rank, world, cap, status, row_vec, bpr,
+                                               static_cast<uint4*>(resid), static_cast<const uint4*>(norm_weight),
+                                               static_cast<float*>(ssq_out))
+                          : cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<false>, t, static_cast<const uint4*>(src),
+                                               static_cast<uint4*>(out), n_vec, rank, world, cap, status, 0, 0,
+                                               static_cast<uint4*>(nullptr), static_cast<const uint4*>(nullptr),
+                                               static_cast<float*>(nullptr));
     return e == cudaSuccess ? AP_OK : comm_fail(e);
+}
+
+}  // namespace
+
+extern "C" int ap_allreduce_residual_blocks(int rows, int row_len) {
+    if (rows < 1 || row_len < 8 || row_len % 8) return 0;
+    const int bpr = (row_len / 8 + 2 * kThreads - 1) / (2 * kThreads);
+    return rows * bpr <= kMaxBlocks ? bpr : 0;
+}
+
+extern "C" int ap_allreduce_oneshot(const void* src, void* out, int count, void* const* peer_buffers, int rank, int world,
+                                    size_t max_payload_bytes, int* status, void* stream) {
+    return allreduce_impl(src, out, count, peer_buffers, rank, world, max_payload_bytes, status, stream, 0, nullptr, nullptr,
+                          nullptr);
+}
+
+extern "C" int ap_allreduce_oneshot_residual(const void* src, void* out, int rows, int row_len, void* resid,
+                                             const void* norm_weight, void* ssq_out, void* const* peer_buffers, int rank,
+                                             int world, size_t max_payload_bytes, int* status, void* stream) {
+    if (!resid) return AP_ERR_NULL_POINTER;
+    if (rows < 1 || row_len < 8) return AP_ERR_BAD_SHAPE;
+    return allreduce_impl(src, out, rows * row_len, peer_buffers, rank, world, max_payload_bytes, status, stream, rows, resid,
+                          norm_weight, ssq_out);
 }

@@ -212,7 +212,19 @@ int ap_gemm_kbit_splitk(const void* x, const void* qweight, int64_t plane_stride
  *   per-call counter, not from the call's size).  Calls of one communication buffer must be
  *   stream-ordered on each rank.  Nothing is allocated or synchronised; the call can be captured
  *   in a CUDA graph and replayed.
+ *   ap_allreduce_oneshot_residual(src, out, rows, row_len, resid, norm_weight, ssq_out, ...)
+ *     the same sum for a row-parallel layer's output [rows][row_len] that a pre-norm decoder adds to its
+ *     residual stream: resid[rows][row_len] (fp16, 16-byte aligned, replicated on the ranks) += fp16(sum) in
+ *     place, out = new resid * norm_weight[row_len] (NOT yet divided by the root mean square), and
+ *     ssq_out[rows][b] (fp32), b < ap_allreduce_residual_blocks(rows, row_len), the sums of squares of the new
+ *     resid over the blocks' ranges: the x, ssq and ssq_blocks of ap_matmul_kbit_prenorm (width = row_len).
+ *     Counts as one call of the sequence above.  ap_allreduce_residual_blocks returns 0 where the shape is not
+ *     supported (rows * blocks above 64).
  */
+int ap_allreduce_residual_blocks(int rows, int row_len);
+int ap_allreduce_oneshot_residual(const void* src, void* out, int rows, int row_len, void* resid, const void* norm_weight,
+                                  void* ssq_out, void* const* peer_buffers, int rank, int world, size_t max_payload_bytes,
+                                  int* status, void* stream);
 size_t ap_comm_buffer_bytes(size_t max_payload_bytes);
 int ap_comm_alloc(size_t bytes, void** ptr);
 int ap_comm_free(void* ptr);

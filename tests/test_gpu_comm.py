@@ -49,6 +49,21 @@ def test_single_rank_roundtrip_and_graph_replay():
     assert not ar.wait_expired()
     with pytest.raises(RuntimeError):
         ar(torch.zeros(128 * 1024, device=dev, dtype=torch.float16))     # 256 KB payload > 128 KB
+    # the form that adds the sum to a residual stream: h += x, out = h * g, partial sums of squares of h
+    for rows, n in ((1, 512), (3, 4096), (8, 8192), (2, 20000)):
+        x = torch.randn((rows, n), device=dev, generator=gen).to(torch.float16)
+        h0 = torch.randn((rows, n), device=dev, generator=gen).to(torch.float16)
+        gw = (1 + 0.1 * torch.randn(n, device=dev, generator=gen)).to(torch.float16)
+        blocks = ar.residual_blocks(rows, n)
+        assert blocks == (n // 8 + 511) // 512
+        h, out = h0.clone(), torch.empty_like(x)
+        ssq = torch.full((rows, blocks), float("nan"), device=dev)
+        ar.residual(x, h, gw, ssq, out)
+        want_h = (h0.float() + x.float()).half()
+        assert torch.equal(h, want_h) and torch.equal(out, (want_h.float() * gw.float()).half())
+        assert torch.allclose(ssq.sum(-1), want_h.float().pow(2).sum(-1), rtol=1e-5)
+    assert ar.residual_blocks(8, 65536) == 0              # 8 rows x 16 blocks: more than the flag table holds
+    assert not ar.wait_expired()
     ar.close()
 
 
@@ -110,6 +125,23 @@ def _rank_main(rank, world, port, result):
             g.replay()
         torch.cuda.synchronize()
         ok = ok and bool((out == float(total * world)).all())
+        # the residual form across ranks, between plain calls of other sizes
+        rows, n = 4, 8192
+        xs = [torch.randn((rows, n), generator=torch.Generator().manual_seed(900 + r)).to(torch.float16) for r in range(world)]
+        h0 = torch.randn((rows, n), generator=torch.Generator().manual_seed(899)).to(torch.float16)
+        gw = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(898))).to(torch.float16)
+        want = torch.zeros((rows, n), dtype=torch.float32)
+        for r in range(world):
+            want += xs[r].float()
+        want_h = (h0.float() + want.half().float()).half()
+        h, out = h0.to(dev), torch.empty((rows, n), device=dev, dtype=torch.float16)
+        ssq = torch.zeros((rows, ar.residual_blocks(rows, n)), device=dev)
+        ar(torch.ones(8, device=dev, dtype=torch.float16))
+        ar.residual(xs[rank].to(dev), h, gw.to(dev), ssq, out)
+        ar(torch.ones(4112, device=dev, dtype=torch.float16))
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(h.cpu(), want_h) and torch.equal(out.cpu(), (want_h.float() * gw.float()).half())
+        ok = ok and torch.allclose(ssq.sum(-1).cpu(), want_h.float().pow(2).sum(-1), rtol=1e-5)
         ok = ok and not ar.wait_expired()
         ar.close()
         result[rank] = ok

@@ -165,12 +165,57 @@ def _decoder_rank(rank, world, port, result):
             for _ in range(3):
                 whole._decode_step()
                 part._decode_step()
-                la = (whole.y.float() @ whole.lm_head.float().T).cpu().numpy()
-                lb = (part.y.float() @ part.lm_head.float().T).cpu().numpy()
+                la, lb = whole.last_logits().cpu().numpy(), part.last_logits().cpu().numpy()
                 ok = ok and _close(lb, la, max_rel=3e-2, mean_abs=5e-3)
                 part.tok.copy_(whole.tok)                      # keep both on the same sequence
             # graph replay with the one-shot all-reduce inside
             out = part.generate(ids, 10, precision=w)
+            gathered = [None] * world
+            dist.all_gather_object(gathered, out.cpu().tolist())
+            ok = ok and all(g == gathered[0] for g in gathered)
+        ok = ok and not ar.wait_expired()
+        ar.close()
+        result[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def _folded_decoder_rank(rank, world, port, result):
+    """A two-rank decoder whose shards the decode kernel takes (so that the residual add + RMSNorm folds into the
+    one-shot all-reduce and the next product): the folded decode step against the same model's unfolded one."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from anyprec_b200.comm import OneShotAllReduce
+        from anyprec_b200.decoder import AnyPrecisionLlama, LlamaSpec
+        spec = LlamaSpec(hidden=512, heads=4, kv_heads=2, ffn=1536, layers=3, vocab=640)
+        B = 2
+        ar = OneShotAllReduce(B * spec.hidden * 2, dev)
+        model = AnyPrecisionLlama.random_init(spec, dev, supported_bits=(3, 4, 8), seed=3, batch=B, max_seq=96,
+                                              tp_rank=rank, tp_world=world, allreduce=ar)
+        model._reduce = lambda t, decode, _ar=ar: _host_sum(t, dist) if not decode else _ar(t)
+        ok = model._folded_norms() and ar.residual_blocks(B, spec.hidden) == 1
+        ids = torch.randint(0, spec.vocab, (B, 24), generator=torch.Generator().manual_seed(8))
+        for w in (3, 8):
+            model.set_precision(w)
+            logits = {}
+            for fold in (False, True):
+                model.fold_norms = fold
+                first = model.prefill(ids)
+                model.tok.copy_(first.argmax(-1))
+                steps = []
+                for _ in range(3):
+                    model._decode_step()
+                    steps.append(model.last_logits().cpu().numpy())
+                logits[fold] = steps
+            for a, b in zip(logits[False], logits[True]):
+                ok = ok and _close(b, a, max_rel=3e-2, mean_abs=5e-3)
+            model._graphs.clear()
+            out = model.generate(ids, 12, precision=w)                  # folded, captured, all-reduce inside
             gathered = [None] * world
             dist.all_gather_object(gathered, out.cpu().tolist())
             ok = ok and all(g == gathered[0] for g in gathered)
@@ -187,6 +232,29 @@ def _host_sum(t, dist):
     dist.all_reduce(c)
     t.copy_(c.to(t.dtype))
     return t
+
+
+def _run_ranks(target, world, timeout=300):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    result = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=timeout)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank did not finish")
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert all(result.get(r) for r in range(world)), dict(result)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_decoder_with_folded_norms():
+    _run_ranks(_folded_decoder_rank, 2)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
