@@ -528,7 +528,8 @@ def decoder_figures(args, device):
     del model
     torch.cuda.empty_cache()
     return {"model": "random-init Llama-2-7B decoder (32 layers, hidden 4096, 32 heads, FFN 11008, vocab 32000), every "
-                     "linear an 8-bit-parent any-precision layer; q+k+v and gate+up stacked; one CUDA graph per precision",
+                     "linear an 8-bit-parent any-precision layer; five launches per layer (q+k+v, attention with rotation and cache write, "
+                     "o, gate+up with SiLU * up, down; residual adds and norms in their epilogues); one CUDA graph per precision",
             "prompt_tokens": prompt, "new_tokens": new, "batch": 1, "per_w_bits": out}
 
 
