@@ -4,18 +4,21 @@
 // rank holds a partial [M][N] fp16 result; the sum over ranks is needed on every rank.  At decode
 // sizes (M*N*2 bytes = 16..128 KB) a ring or tree collective is all latency, so here every rank
 //   1. stores its partial into slot `rank` of an inbox on EVERY rank (plain 16-byte stores through
-//      NVLink / NVSwitch peer mappings, nothing else),
-//   2. publishes the call's sequence number, per block, on every rank (release, system scope),
-//   3. waits until the same block of every rank has published that number (acquire, bounded),
-//   4. adds the `world` slots of its own inbox in rank order with fp32 accumulation and writes fp16.
+//      NVLink / NVSwitch peer mappings, nothing else).  Every 16-byte store carries 8 bytes of payload and
+//      the call's sequence number twice: {word, seq, word, seq}.  An aligned 8-byte half of a store
+//      arrives whole, so a reader that finds the number beside a word knows the word is this call's:
+//      no fence, no separate flag, one trip over the link;
+//   2. polls the `world` slots of its own inbox (volatile loads, bounded) until every line of its
+//      share carries the call's number, adds them in rank order with fp32 accumulation and writes fp16.
 // The rank order is the same everywhere, so all ranks end with bit-identical results.
 //
 // Memory: one communication buffer per rank, allocated here with cudaMalloc and exchanged between
 // the processes of one node as CUDA IPC handles (ap_comm_* below).  Layout of a buffer:
 //   [0, 4 KB)           header (private): word 0 = calls completed, word 1 = blocks of the running
 //                       call that are done, word 2 = error word
-//   [4 KB, 20 KB)       flags[kMaxWorld][kMaxBlocks] written by the peers, 32 bytes apart
-//   then                inbox[2][kMaxWorld][cap]    two generations, used in turn
+//   [4 KB, 20 KB)       unused (kept so that the inbox stays where it was)
+//   then                inbox[2][kMaxWorld][2 * cap]    two generations, used in turn; 2 * cap because half
+//                       of every line is sequence numbers
 // The call counter lives on the device, so a captured CUDA graph can be replayed: every block of a
 // launch reads it (after the previous kernel in the stream is over), the call's number is that
 // plus one, and the block that finishes last writes it back.  All ranks advance in step because
@@ -23,12 +26,13 @@
 // same for every block of a call whatever its size, so consecutive calls always alternate
 // generations even when their element counts (and with them the number of blocks and each
 // block's range) differ.  Two generations are enough: a rank finishes call c only after it has
-// seen a flag of call c from every rank, a rank publishes its first flag of call c only after
-// all of its call c-1 is over (stream order), so when a fast rank stores call c+1 into the
-// generation that call c-1 used, every rank is done reading call c-1.
+// read call c's lines from every rank, a rank stores its first line of call c only after all of its
+// call c-1 is over (stream order), so when a fast rank stores call c+1 into the generation that
+// call c-1 used, every rank is done reading call c-1.  Sequence numbers start at 1 and the buffer
+// starts zeroed, so a line never carries a call's number before that call wrote it.
 //
 // Every wait is bounded.  When one runs out the block records it in `status` (if given) and in the
-// buffer's own error word, skips the reduction and returns; nothing can spin forever.
+// buffer's own error word and returns without a result; nothing can spin forever.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -46,25 +50,23 @@ constexpr int kThreads = 256;
 constexpr size_t kSeqBytes = 4096;
 constexpr size_t kFlagBytes = (size_t)kMaxWorld * kMaxBlocks * sizeof(uint32_t) * 8;   // padded: 32 B per flag
 constexpr size_t kHeaderBytes = kSeqBytes + kFlagBytes;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 21;                  // polls of a thread's lines before it gives up (seconds)
+constexpr int kVecPerBlock = kThreads;                     // payload vectors (16 bytes) per block: one per thread
 
 struct PeerTable {
     unsigned char* buf[kMaxWorld];
 };
 
-__device__ __forceinline__ uint32_t* flag_slot(unsigned char* base, int from_rank, int block) {
-    return reinterpret_cast<uint32_t*>(base + kSeqBytes + ((size_t)from_rank * kMaxBlocks + block) * 32);
-}
+// lines of (generation, sender): payload vector v is lines 2v and 2v + 1
 __device__ __forceinline__ uint4* inbox_slot(unsigned char* base, int gen, int from_rank, size_t cap) {
-    return reinterpret_cast<uint4*>(base + kHeaderBytes + ((size_t)gen * kMaxWorld + from_rank) * cap);
+    return reinterpret_cast<uint4*>(base + kHeaderBytes + ((size_t)gen * kMaxWorld + from_rank) * 2 * cap);
 }
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_line(uint4* p, uint32_t a, uint32_t b, uint32_t seq) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(a), "r"(seq), "r"(b) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_line(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
@@ -90,7 +92,6 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
     unsigned char* mine = peers.buf[rank];
     uint32_t* header = reinterpret_cast<uint32_t*>(mine);      // [0] calls, [1] blocks done, [2] error
     __shared__ uint32_t s_seq;
-    __shared__ int s_ok;
     // Launched as a programmatic dependent of the kernel that produces `src` (the row-parallel
     // matmul_kbit), so that this kernel's launch overlaps that kernel's tail; the next kernel in the
     // stream may start its own prologue now and finds `out` complete when its dependency wait
@@ -98,10 +99,7 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
     // written by the previous call of this kernel, which is only known to be over after it.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (threadIdx.x == 0) {
-        s_seq = __ldcg(header) + 1u;
-        s_ok = 1;
-    }
+    if (threadIdx.x == 0) s_seq = __ldcg(header) + 1u;
     __syncthreads();
     const uint32_t seq = s_seq;
     const int gen = seq & 1u;
@@ -120,27 +118,6 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
         v1 = (v0 + per_block < n_vec) ? (v0 + per_block) : n_vec;
     }
 
-    // 1. push
-    for (int v = v0 + threadIdx.x; v < v1; v += kThreads) {
-        const uint4 val = src[v];
-        for (int p = 0; p < world; p++) inbox_slot(peers.buf[p], gen, rank, cap)[v] = val;
-    }
-    __threadfence_system();
-    __syncthreads();
-    // 2. publish, 3. wait
-    if (threadIdx.x < world) {
-        const int p = threadIdx.x;
-        st_release_sys(flag_slot(peers.buf[p], rank, blockIdx.x), seq);
-        const uint32_t* theirs = flag_slot(mine, p, blockIdx.x);
-        bool seen = false;
-        for (uint32_t i = 0; i < kSpinLimit; i++) {
-            // a peer can be one call ahead of this rank, never behind by more than this call
-            const uint32_t f = ld_acquire_sys(theirs);
-            if (f == seq || f == seq + 1u) { seen = true; break; }
-        }
-        if (!seen) atomicExch(&s_ok, 0);
-    }
-    __syncthreads();
     // Every block reads the call counter before it gets here, so the block that counts itself
     // last may advance it: the next call (after this kernel in stream order) then sees seq.
     auto finish = [&]() {
@@ -152,23 +129,44 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
             }
         }
     };
-    if (!s_ok) {
-        if (threadIdx.x == 0) {
-            if (status) atomicExch(status, 1);
-            header[2] = 1u;                                         // the buffer's own error word
-        }
-        finish();                                                   // stay in step with the other ranks
-        return;
-    }
-    // 4. reduce in rank order
-    float sq = 0.f;
+    // 1. push: this thread's vectors, to every rank
     for (int v = v0 + threadIdx.x; v < v1; v += kThreads) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const uint4 val = src[v];
         for (int p = 0; p < world; p++) {
-            const uint4 q = __ldcv(inbox_slot(mine, gen, p, cap) + v);
-            const float2 a = h2f(q.x), b = h2f(q.y), c = h2f(q.z), d = h2f(q.w);
-            acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-            acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+            uint4* line = inbox_slot(peers.buf[p], gen, rank, cap) + 2 * (size_t)v;
+            st_line(line, val.x, val.y, seq);
+            st_line(line + 1, val.z, val.w, seq);
+        }
+    }
+    // 2. poll the same vectors' lines from every rank, add in rank order
+    float sq = 0.f;
+    bool ok = true;
+    for (int v = v0 + threadIdx.x; v < v1 && ok; v += kThreads) {
+        uint4 la[kMaxWorld], lb[kMaxWorld];
+        bool ready = false;
+        for (uint32_t spin = 0; spin < kSpinLimit && !ready; spin++) {
+            ready = true;
+#pragma unroll
+            for (int p = 0; p < kMaxWorld; p++) {
+                if (p < world) {
+                    const uint4* line = inbox_slot(mine, gen, p, cap) + 2 * (size_t)v;
+                    la[p] = ld_line(line);
+                    lb[p] = ld_line(line + 1);
+                }
+            }
+#pragma unroll
+            for (int p = 0; p < kMaxWorld; p++)
+                if (p < world) ready = ready && la[p].y == seq && la[p].w == seq && lb[p].y == seq && lb[p].w == seq;
+        }
+        if (!ready) { ok = false; break; }
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int p = 0; p < kMaxWorld; p++) {
+            if (p < world) {
+                const float2 a = h2f(la[p].x), b = h2f(la[p].z), c = h2f(lb[p].x), d = h2f(lb[p].z);
+                acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+                acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+            }
         }
         uint4 r;
         r.x = f2h(acc[0], acc[1]);
@@ -194,6 +192,10 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
         } else {
             out[v] = r;
         }
+    }
+    if (!ok) {                                               // a peer's lines never came: say so, stay in step
+        if (status) atomicExch(status, 1);
+        header[2] = 1u;                                      // the buffer's own error word
     }
     if constexpr (RES) {
         // the block's sum of squares in a fixed order: shuffle tree, then the warps' sums left to right
@@ -222,7 +224,7 @@ int comm_fail(cudaError_t e) {
 
 extern "C" size_t ap_comm_buffer_bytes(size_t max_payload_bytes) {
     const size_t cap = (max_payload_bytes + 255) & ~static_cast<size_t>(255);
-    return kHeaderBytes + 2 * static_cast<size_t>(kMaxWorld) * cap;
+    return kHeaderBytes + 2 * static_cast<size_t>(kMaxWorld) * 2 * cap;
 }
 
 extern "C" int ap_comm_alloc(size_t bytes, void** ptr) {
@@ -282,7 +284,7 @@ int allreduce_impl(const void* src, void* out, int count, void* const* peer_buff
     }
     const int n_vec = count / 8;
     // the same grid on every rank for a given count: blocks of different ranks pair up by index
-    int blocks = (n_vec + 2 * kThreads - 1) / (2 * kThreads);
+    int blocks = (n_vec + kVecPerBlock - 1) / kVecPerBlock;
     blocks = blocks < 1 ? 1 : (blocks > kMaxBlocks ? kMaxBlocks : blocks);
     int row_vec = 0, bpr = 0;
     if (resid) {
@@ -320,7 +322,7 @@ int allreduce_impl(const void* src, void* out, int count, void* const* peer_buff
 
 extern "C" int ap_allreduce_residual_blocks(int rows, int row_len) {
     if (rows < 1 || row_len < 8 || row_len % 8) return 0;
-    const int bpr = (row_len / 8 + 2 * kThreads - 1) / (2 * kThreads);
+    const int bpr = (row_len / 8 + kVecPerBlock - 1) / kVecPerBlock;
     return rows * bpr <= kMaxBlocks ? bpr : 0;
 }
 

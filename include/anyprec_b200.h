@@ -189,9 +189,9 @@ int ap_gemm_kbit_splitk(const void* x, const void* qweight, int64_t plane_stride
 /*
  * Tensor parallelism: one-shot all-reduce (sum) of the fp16 outputs of row-parallel layers over
  * peer memory.  No counterpart in the reference (single device).  Every rank stores its partial
- * result into an inbox on every rank, publishes a sequence number, waits (bounded) for the other
- * ranks' numbers and adds the inbox slots in rank order with fp32 accumulation, so that all ranks
- * end with identical bits.  For the ranks of ONE node, one process per GPU.
+ * result into an inbox on every rank, every 16-byte store carrying the call's sequence number beside
+ * its 8 bytes of payload, polls (bounded) its own inbox until all ranks' lines carry that number and adds
+ * them in rank order with fp32 accumulation, so that all ranks end with identical bits.  For the ranks of ONE node, one process per GPU.
  *
  * Set-up (these calls allocate, synchronise and are not for the serving loop):
  *   ap_comm_buffer_bytes(max_payload)  size of a rank's communication buffer for payloads of up to

@@ -198,7 +198,7 @@ def _folded_decoder_rank(rank, world, port, result):
         model = AnyPrecisionLlama.random_init(spec, dev, supported_bits=(3, 4, 8), seed=3, batch=B, max_seq=96,
                                               tp_rank=rank, tp_world=world, allreduce=ar)
         model._reduce = lambda t, decode, _ar=ar: _host_sum(t, dist) if not decode else _ar(t)
-        ok = model._folded_norms() and ar.residual_blocks(B, spec.hidden) == 1
+        ok = model._folded_norms() and ar.residual_blocks(B, spec.hidden) == 1           # 64 vectors per row
         ids = torch.randint(0, spec.vocab, (B, 24), generator=torch.Generator().manual_seed(8))
         for w in (3, 8):
             model.set_precision(w)
