@@ -80,7 +80,7 @@ def test_split_k_and_all_reduce_entry_points_check_their_arguments(lib):
     assert lib.ap_gemm_kbit_workspace_bytes(64, 4096, 1) == 0
     assert lib.ap_gemm_kbit_workspace_bytes(64, 4096, 4) == 64 * 1024 + 4 * 64 * 4096 * 4
     # communication buffer: header + two generations of eight inbox slots
-    assert lib.ap_comm_buffer_bytes(1000) == 20480 + 2 * 8 * 1024
+    assert lib.ap_comm_buffer_bytes(1000) == 20480 + 2 * 8 * 2 * 1024      # half of every inbox line is sequence numbers
     buf = ctypes.create_string_buffer(8192)
     base = (ctypes.cast(buf, vp).value + 255) & ~255
     table = (vp * 2)(base, base)
