@@ -18,8 +18,8 @@
 //   6. the parent-precision cluster index of every weight, in its original position, is its code
 //      (:171-180).
 // The arithmetic is written with explicit round-to-nearest fp64 intrinsics so that no multiply-add is
-// fused, and the prefix sums add in a fixed blocked order (each of the 1024 threads its run of
-// consecutive positions left to right, then the runs' totals left to right, then offset + local sum):
+// fused, and the prefix sums add in a fixed blocked order (1024 runs of consecutive positions, each left
+// to right, then the runs' totals left to right, then offset + local sum):
 // the CPU checker restates exactly this order and the results agree bit for bit.
 //
 // Shared memory: the sort keys (4 bytes) and original positions (2 bytes) of the row padded to a
@@ -33,7 +33,7 @@
 
 namespace {
 
-constexpr int kThreads = 1024;
+constexpr int kRuns = 1024;                                // runs of the blocked prefix sums (fixed: it defines the rounding)
 constexpr int kMaxClusters = 256;
 
 __device__ __forceinline__ uint32_t key_of(float x) {
@@ -63,51 +63,65 @@ __device__ __forceinline__ int count_le(const uint32_t* keys, int start, int sto
     return lo;
 }
 
-// Split of the non-empty cluster [start, stop): centroids of the two sides and the split position.
-__device__ void two_cluster(const uint32_t* keys, const double* wp, const double* wxp, int start,
-                            int stop, double& c0, double& c1, int& division) {
+// Split of the non-empty cluster [start, stop): centroids of the two sides and the split position.  The sums over
+// [start, d) and [d, stop) are prefix[d - 1] - prefix[start - 1] and prefix[stop - 1] - prefix[d - 1]: the two ends
+// are read once, and every step of the search has its two loads (weights, weights * values at d - 1) in flight
+// together, one trip to L2 per step.
+__device__ void two_cluster(const uint32_t* keys, const double* wp, const double* wxp, int start, int stop, double& c0,
+                            double& c1, int& division) {
     if (stop - start == 1) {
         c0 = c1 = (double)val_of(keys[start]);
         division = stop;
         return;
     }
+    const double w_lo = start > 0 ? __ldcg(wp + start - 1) : 0.0, x_lo = start > 0 ? __ldcg(wxp + start - 1) : 0.0;
+    const double w_hi = __ldcg(wp + stop - 1), x_hi = __ldcg(wxp + stop - 1);
+    // sums of [start, d) and [d, stop) from the prefix values at d - 1 (d > start, so d - 1 >= 0)
+    auto left = [&](double at, double lo) { return start > 0 ? __dsub_rn(at, lo) : at; };
     int lo = start + 1, hi = stop - 1;
     while (lo < hi) {
         const int d = (lo + hi) >> 1;
-        const double wl = range_sum(wp, start, d), wr = range_sum(wp, d, stop);
+        const double w_at = __ldcg(wp + d - 1), x_at = __ldcg(wxp + d - 1);
+        const double wl = left(w_at, w_lo), wr = __dsub_rn(w_hi, w_at);
         bool move_right;
         if (wl <= 0.0) move_right = true;
         else if (wr <= 0.0) move_right = false;
         else {
-            const double mid = __dmul_rn(__dadd_rn(__ddiv_rn(range_sum(wxp, start, d), wl), __ddiv_rn(range_sum(wxp, d, stop), wr)), 0.5);
+            const double mid = __dmul_rn(__dadd_rn(__ddiv_rn(left(x_at, x_lo), wl), __ddiv_rn(__dsub_rn(x_hi, x_at), wr)), 0.5);
             move_right = (double)val_of(keys[d]) <= mid;
         }
         if (move_right) lo = d + 1;
         else hi = d;
     }
     const int d = lo;
-    const double wl = range_sum(wp, start, d), wr = range_sum(wp, d, stop);
-    c0 = wl > 0.0 ? __ddiv_rn(range_sum(wxp, start, d), wl) : (double)val_of(keys[d - 1]);
-    c1 = wr > 0.0 ? __ddiv_rn(range_sum(wxp, d, stop), wr) : (double)val_of(keys[d]);
+    const double w_at = __ldcg(wp + d - 1), x_at = __ldcg(wxp + d - 1);
+    const double wl = left(w_at, w_lo), wr = __dsub_rn(w_hi, w_at);
+    c0 = wl > 0.0 ? __ddiv_rn(left(x_at, x_lo), wl) : (double)val_of(keys[d - 1]);
+    c1 = wr > 0.0 ? __ddiv_rn(__dsub_rn(x_hi, x_at), wr) : (double)val_of(keys[d]);
     division = d;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+// THREADS: 1024, one block per SM, or 512, two per SM, for rows short enough that two fit the shared memory: most
+// of a row's time is spent in steps that keep one thread per cluster busy and wait on L2, which a second block
+// overlaps.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 seed_upscale_kernel(const float* __restrict__ weight, const float* __restrict__ sens, int N, int K, int Kpad, int seed_bit,
                     int parent_bit, int max_iter, uint8_t* __restrict__ codes, __half* __restrict__ luts, double* __restrict__ work) {
     extern __shared__ __align__(16) unsigned char smem[];
     uint32_t* keys = reinterpret_cast<uint32_t*>(smem);
     uint16_t* idx = reinterpret_cast<uint16_t*>(smem + (size_t)Kpad * 4);
-    double* tot = reinterpret_cast<double*>(smem + (size_t)Kpad * 6);           // [3][kThreads]: w, w * x, x
-    double* cent = tot + 3 * kThreads;                                           // [kMaxClusters]
+    constexpr int kThreads = THREADS;
+    static_assert(THREADS > kMaxClusters && kRuns % THREADS == 0, "one thread per cluster border; whole runs per thread");
+    double* tot = reinterpret_cast<double*>(smem + (size_t)Kpad * 6);           // [3][kRuns]: w, w * x, x
+    double* cent = tot + 3 * kRuns;                                              // [kMaxClusters]
     float* level = reinterpret_cast<float*>(cent + kMaxClusters);                // [2][kMaxClusters] fp32 tables
     int* bord = reinterpret_cast<int*>(level + 2 * kMaxClusters);                // [2][kMaxClusters + 4]
     constexpr int kBordStride = kMaxClusters + 4;
     const int tid = threadIdx.x;
     double* wp = work + (size_t)blockIdx.x * 2 * K;
     double* wxp = wp + K;
-    const int run = (K + kThreads - 1) / kThreads;
-    const int r0 = tid * run < K ? tid * run : K, r1 = (tid + 1) * run < K ? (tid + 1) * run : K;
+    const int run = (K + kRuns - 1) / kRuns;                 // positions per run; run r is [r * run, (r + 1) * run) cut at K
 
     for (int row = blockIdx.x; row < N; row += gridDim.x) {
         const float* xr = weight + (size_t)row * K;
@@ -134,7 +148,8 @@ seed_upscale_kernel(const float* __restrict__ weight, const float* __restrict__ 
             }
         }
         // ---- 3. prefix sums: totals of every thread's run, their exclusive scan, then offset + local sum
-        {
+        for (int r = tid; r < kRuns; r += kThreads) {
+            const int r0 = r * run < K ? r * run : K, r1 = (r + 1) * run < K ? (r + 1) * run : K;
             double tw = 0.0, twx = 0.0, tx = 0.0;
             for (int e = r0; e < r1; e++) {
                 const float x = val_of(keys[e]);
@@ -143,15 +158,15 @@ seed_upscale_kernel(const float* __restrict__ weight, const float* __restrict__ 
                 twx = __dadd_rn(twx, __dmul_rn((double)x, (double)w));
                 tx = __dadd_rn(tx, (double)x);
             }
-            tot[tid] = tw;
-            tot[kThreads + tid] = twx;
-            tot[2 * kThreads + tid] = tx;
+            tot[r] = tw;
+            tot[kRuns + r] = twx;
+            tot[2 * kRuns + r] = tx;
         }
         __syncthreads();
         if (tid < 3) {
             double acc = 0.0;
-            double* t = tot + tid * kThreads;
-            for (int i = 0; i < kThreads; i++) {
+            double* t = tot + tid * kRuns;
+            for (int i = 0; i < kRuns; i++) {
                 const double v = t[i];
                 t[i] = acc;
                 acc = __dadd_rn(acc, v);
@@ -161,9 +176,10 @@ seed_upscale_kernel(const float* __restrict__ weight, const float* __restrict__ 
         __syncthreads();
         const bool unweighted = cent[0] == 0.0;
         __syncthreads();
-        {
+        for (int r = tid; r < kRuns; r += kThreads) {
+            const int r0 = r * run < K ? r * run : K, r1 = (r + 1) * run < K ? (r + 1) * run : K;
             double lw = 0.0, lwx = 0.0;
-            const double ow = tot[tid], owx = unweighted ? tot[2 * kThreads + tid] : tot[kThreads + tid];
+            const double ow = tot[r], owx = unweighted ? tot[2 * kRuns + r] : tot[kRuns + r];
             for (int e = r0; e < r1; e++) {
                 const float x = val_of(keys[e]);
                 if (unweighted) {
@@ -207,8 +223,8 @@ seed_upscale_kernel(const float* __restrict__ weight, const float* __restrict__ 
         __syncthreads();
         if (tid < k0) {
             const int a = b_cur[tid], b = b_cur[tid + 1];
-            const double ws = range_sum(wp, a, b);
-            cent[tid] = ws > 0.0 ? __ddiv_rn(range_sum(wxp, a, b), ws) : (double)val_of(keys[a < K - 1 ? a : K - 1]);
+            const double ws = range_sum(wp, a, b), xs = range_sum(wxp, a, b);       // both requested together
+            cent[tid] = ws > 0.0 ? __ddiv_rn(xs, ws) : (double)val_of(keys[a < K - 1 ? a : K - 1]);
         }
         __syncthreads();
         for (int it = 0; it < max_iter; it++) {
@@ -231,8 +247,8 @@ seed_upscale_kernel(const float* __restrict__ weight, const float* __restrict__ 
             __syncthreads();
             if (tid < k0) {
                 const int a = b_cur[tid], b = b_cur[tid + 1];
-                const double ws = range_sum(wp, a, b);
-                if (ws > 0.0) cent[tid] = __ddiv_rn(range_sum(wxp, a, b), ws);
+                const double ws = range_sum(wp, a, b), xs = range_sum(wxp, a, b);
+                if (ws > 0.0) cent[tid] = __ddiv_rn(xs, ws);
             }
             __syncthreads();
         }
@@ -291,7 +307,7 @@ seed_upscale_kernel(const float* __restrict__ weight, const float* __restrict__ 
 }
 
 size_t smem_bytes(int Kpad) {
-    return (size_t)Kpad * 6 + 3 * kThreads * sizeof(double) + kMaxClusters * sizeof(double) + 2 * kMaxClusters * sizeof(float) +
+    return (size_t)Kpad * 6 + 3 * kRuns * sizeof(double) + kMaxClusters * sizeof(double) + 2 * kMaxClusters * sizeof(float) +
            2 * (kMaxClusters + 4) * sizeof(int);
 }
 
@@ -323,9 +339,15 @@ extern "C" int ap_seed_upscale(const void* weight, const void* sensitivity, int 
     if (blocks > (size_t)N) blocks = N;
     const int Kpad = padded(K);
     const size_t smem = smem_bytes(Kpad);
-    cudaError_t e = cudaFuncSetAttribute(seed_upscale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // two blocks of 512 threads per SM where two rows fit the shared memory (with all of it carved out for shared
+    // memory: the driver's default carve-out left room for one)
+    const bool two = 2 * (smem + 1024) <= 227 * 1024;
+    auto kernel = two ? seed_upscale_kernel<512> : seed_upscale_kernel<1024>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return AP_ERR_LAUNCH;
-    seed_upscale_kernel<<<(unsigned)blocks, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return AP_ERR_LAUNCH;
+    kernel<<<(unsigned)blocks, two ? 512 : 1024, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const float*>(weight), static_cast<const float*>(sensitivity), N, K, Kpad, seed_bits, parent_bits, max_iter,
         static_cast<uint8_t*>(codes), static_cast<__half*>(luts), static_cast<double*>(workspace));
     return cudaGetLastError() == cudaSuccess ? AP_OK : AP_ERR_LAUNCH;

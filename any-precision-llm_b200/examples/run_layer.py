@@ -4,7 +4,8 @@
 
 `--reps` distinct random layers are created (uniform parent codes drawn as random bitplanes, sorted
 N(0, 0.02) fp16 tables) and the chosen operator is called once on each:
-`matmul` = any_precision_ext.matmul_kbit (decode GEMV), `gemm` = gemm_kbit (fused prefill),
+`matmul` = any_precision_ext.matmul_kbit (decode GEMV), `prenorm` = the same product through the decoder variant
+of the kernel (scaled by rsqrt of a given mean square in its epilogue), `gemm` = gemm_kbit (fused prefill),
 `dequant` = dequant_kbit, `quantize` = quantize.seed_and_upscale_layer (seed 3 bits, parent 8; random fp16-valued
 weights and squared-normal sensitivities instead of packed operands).  Prints the mean |y| of the last result so the work cannot be elided.
 """
@@ -22,7 +23,7 @@ from anyprec_b200 import packing
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["matmul", "gemm", "dequant", "quantize"], default="matmul")
+    ap.add_argument("--op", choices=["matmul", "prenorm", "gemm", "dequant", "quantize"], default="matmul")
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--w", type=int, default=4)
@@ -44,10 +45,13 @@ def main():
     qs = [packing.random_qweight(8, a.N, a.K, device="cuda", generator=gen) for _ in range(a.reps)]
     luts = [packing.random_lut(a.N, a.w, device="cuda", generator=gen) for _ in range(a.reps)]
     x = torch.randn((a.M, a.K), device="cuda", generator=gen).half()
+    ssq = torch.full((a.M, a.K // 16), 16.0, device="cuda")                # mean square 1
     y = None
     for q, lut in zip(qs, luts):
         if a.op == "matmul":
             y = ext.matmul_kbit(x, q, lut, a.w)
+        elif a.op == "prenorm":
+            y = ext.matmul_kbit(x, q, lut, a.w, prenorm=(ssq, a.K, 1e-5))
         elif a.op == "gemm":
             y = ext.gemm_kbit(x, q, lut, a.w)
         else:
