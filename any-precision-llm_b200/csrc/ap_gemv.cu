@@ -154,7 +154,34 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
     // `valid` false (a word past the end of a short last group): the weights are taken as zero
     // without looking anything up, so that no table entry, finite or not, meets the (zeroed) activations.
     using Cfg = GemvCfg<W>;
-    if constexpr (MODE == 2 || Cfg::kRegLut) {
+    if constexpr (MODE == 2) {
+        // Pair tables: byte (3 - j) of na[c] / nb[c] is the index of the weight pair (e = 3 - c, e = 7 - c) of byte
+        // group j.  One byte group at a time: eight lookups, four activation pairs, two MMAs, so that only eight
+        // looked-up words are alive at once.
+        uint32_t na[4], nb[4];
+        transpose_nibbles<W>(wa, na);
+        transpose_nibbles<W>(wb, nb);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t qa[4], qb[4];                           // fp16x2 (W[e = 7-c], W[e = 3-c]) of rows g and g + 8
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                qa[c] = valid ? lds_u32(tab_const + entry_offset_direct(na[c], 3 - j, tab_a)) : 0u;
+                qb[c] = valid ? lds_u32(tab_const + entry_offset_direct(nb[c], 3 - j, tab_b)) : 0u;
+            }
+            // activations paired the same way: xq[c] = (x[7-c], x[3-c])
+            uint32_t xq[4];
+            xq[0] = __byte_perm(xv[j].w, xv[j].y, 0x7632);
+            xq[1] = __byte_perm(xv[j].w, xv[j].y, 0x5410);
+            xq[2] = __byte_perm(xv[j].z, xv[j].x, 0x7632);
+            xq[3] = __byte_perm(xv[j].z, xv[j].x, 0x5410);
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+                mma16816(acc[h], qa[2 * h], qb[2 * h], qa[2 * h + 1], qb[2 * h + 1], xq[2 * h], xq[2 * h + 1]);
+        }
+    } else if constexpr (Cfg::kRegLut) {
+        // w = 3 without pair tables: the row's eight table entries live in four registers and a byte permute with
+        // the nibble codes as selectors is the lookup.
         uint32_t na[4], nb[4];
         transpose_nibbles<W>(wa, na);
         transpose_nibbles<W>(wb, nb);
@@ -162,34 +189,21 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
         uint32_t wq[2][4][4];
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            if constexpr (MODE == 2) {
-                if (valid) {
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        wq[0][c][j] = lds_u32(tab_const + entry_offset_direct(na[c], 3 - j, tab_a));
-                        wq[1][c][j] = lds_u32(tab_const + entry_offset_direct(nb[c], 3 - j, tab_b));
-                    }
-                } else {
+            for (int hs = 0; hs < 2; hs++) {     // selector half: nibbles of byte groups (3,2) then (1,0)
+                const uint32_t sa = hs ? (na[c] >> 16) : na[c], sb = hs ? (nb[c] >> 16) : nb[c];
+                const uint32_t alo = __byte_perm(lut_lo[0][0], lut_lo[0][1], sa);
+                const uint32_t ahi = __byte_perm(lut_hi[0][0], lut_hi[0][1], sa);
+                const uint32_t blo = __byte_perm(lut_lo[1][0], lut_lo[1][1], sb);
+                const uint32_t bhi = __byte_perm(lut_hi[1][0], lut_hi[1][1], sb);
+                wq[0][c][3 - 2 * hs] = __byte_perm(alo, ahi, 0x5140);
+                wq[0][c][2 - 2 * hs] = __byte_perm(alo, ahi, 0x7362);
+                wq[1][c][3 - 2 * hs] = __byte_perm(blo, bhi, 0x5140);
+                wq[1][c][2 - 2 * hs] = __byte_perm(blo, bhi, 0x7362);
+            }
+            if (!valid) {
 #pragma unroll
-                    for (int j = 0; j < 4; j++) wq[0][c][j] = wq[1][c][j] = 0u;
-                }
-            } else {
-#pragma unroll
-                for (int hs = 0; hs < 2; hs++) {     // selector half: nibbles of byte groups (3,2) then (1,0)
-                    const uint32_t sa = hs ? (na[c] >> 16) : na[c], sb = hs ? (nb[c] >> 16) : nb[c];
-                    const uint32_t alo = __byte_perm(lut_lo[0][0], lut_lo[0][1], sa);
-                    const uint32_t ahi = __byte_perm(lut_hi[0][0], lut_hi[0][1], sa);
-                    const uint32_t blo = __byte_perm(lut_lo[1][0], lut_lo[1][1], sb);
-                    const uint32_t bhi = __byte_perm(lut_hi[1][0], lut_hi[1][1], sb);
-                    wq[0][c][3 - 2 * hs] = __byte_perm(alo, ahi, 0x5140);
-                    wq[0][c][2 - 2 * hs] = __byte_perm(alo, ahi, 0x7362);
-                    wq[1][c][3 - 2 * hs] = __byte_perm(blo, bhi, 0x5140);
-                    wq[1][c][2 - 2 * hs] = __byte_perm(blo, bhi, 0x7362);
-                }
-                if (!valid) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) wq[0][c][j] = wq[1][c][j] = 0u;
-                }
+                for (int j = 0; j < 4; j++) wq[0][c][j] = wq[1][c][j] = 0u;
             }
         }
 #pragma unroll
