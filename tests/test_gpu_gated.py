@@ -111,12 +111,13 @@ def test_gated_refuses_what_the_kernel_does_not_take():
 
 
 @pytest.mark.parametrize("M", [1, 5, 8])
-@pytest.mark.parametrize("splits", [1, 3])
-def test_residual_and_prenorm_products_fold_add_and_rmsnorm(M, splits):
+@pytest.mark.parametrize("splits,H,K1", [(1, 256, 1024), (3, 256, 1024), (2, 384, 11008), (1, 128, 1152)])
+def test_residual_and_prenorm_products_fold_add_and_rmsnorm(M, splits, H, K1):
     """h += linear_1(x); z = linear_2(rmsnorm(h) * g) as two launches (ap_matmul_kbit_residual,
-    ap_matmul_kbit_prenorm) against the same chain with the add and the norm written out."""
+    ap_matmul_kbit_prenorm) against the same chain with the add and the norm written out; row lengths with a
+    short last group (11008, 1152) and a width that is not a power of two (384) among them."""
     import any_precision_ext as ext
-    H, K1, F = 256, 1024, 192
+    F = 192
     c1, l1 = make_layer(H, K1, seed=41)
     c2, l2 = make_layer(F, H, seed=42)
     q1, q2 = dev(oracle.pack(c1)), dev(oracle.pack(c2))
