@@ -618,7 +618,8 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
     splits = (chunks + split_chunks - 1) / split_chunks;
     *used = true;
     // Three blocks per SM (80 registers) only where two per SM could not hold the launch at once and
-    // the table leaves room for enough chunk buffers: measured, that is w <= 5 from about 450 blocks on.
+    // the table leaves room for enough chunk buffers: measured, that is w = 3 (and w = 4 above two batch rows)
+    // from about 450 blocks on; everywhere else, w = 5 included, it loses.
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -635,9 +636,6 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
         AP_TMA_GO(2, 2);
     } else if constexpr (W == 4) {
         if (M <= 2) AP_TMA_GO(2, 2);
-        if (many_blocks) AP_TMA_GO(3, 1);
-        AP_TMA_GO(2, 1);
-    } else if constexpr (W == 5) {
         if (many_blocks) AP_TMA_GO(3, 1);
         AP_TMA_GO(2, 1);
     } else if constexpr (W <= 7) {
