@@ -70,6 +70,9 @@ def load_library() -> ctypes.CDLL:
     lib.ap_matmul_kbit_gated.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, vp]
     lib.ap_matmul_kbit_prenorm.restype = i
     lib.ap_matmul_kbit_prenorm.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, i, vp, i, i, ctypes.c_float, vp]
+    lib.ap_matmul_kbit_push.restype = i
+    lib.ap_matmul_kbit_push.argtypes = [vp, vp, i64, vp, i, i, i, i, i, vp, ctypes.c_size_t, ctypes.POINTER(vp), i, i,
+                                        ctypes.c_size_t, vp]
     lib.ap_matmul_kbit_residual.restype = i
     lib.ap_matmul_kbit_residual.argtypes = [vp, vp, i64, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, vp, vp, vp, vp]
     lib.ap_silu_mul.restype = i
@@ -260,7 +263,7 @@ def reserve_workspace(device=None, nbytes: int = _MIN_WORKSPACE) -> int:
 
 def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bits: int, *,
                 out: torch.Tensor | None = None, splits: int | None = None, gated: bool = False,
-                prenorm=None, residual=None):
+                prenorm=None, residual=None, push=None):
     """``x @ W_w.T`` for fp16 ``x[..., K]``; returns fp16 ``[..., N]``.
 
     Same call as the reference's ``matmul_kbit`` (kernels/main.cu:93-143).  ``splits`` (default:
@@ -275,6 +278,9 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
     ``[rows, N / 16]``); the second takes that as ``x`` and scales its result by
     ``rsqrt(sum(ssq) / width + eps)`` (``ap_matmul_kbit_residual`` / ``ap_matmul_kbit_prenorm``; a
     fourth entry of ``prenorm`` gives the number of partial sums per row when another kernel wrote them).
+    ``push=comm.OneShotAllReduce(...).push_target`` (tensor parallelism): the product is a row-parallel
+    layer's partial result and goes straight into the all-reduce inboxes of all ranks instead of a tensor
+    (``ap_matmul_kbit_push``; returns None; ``OneShotAllReduce.collect`` must follow).
     """
     N, K, plane_stride = _check_operands(qweight, lut, w_bits)
     if x.dtype != torch.float16:
@@ -293,6 +299,21 @@ def matmul_kbit(x: torch.Tensor, qweight: torch.Tensor, lut: torch.Tensor, w_bit
     if M == 0:
         return torch.empty((*lead, N), dtype=torch.float16, device=x.device)
     lib = load_library()
+    if push is not None:
+        if gated or prenorm is not None or residual is not None or out is not None or M > 8 or N % 16:
+            raise ValueError("push= goes with a plain product of at most eight rows and N % 16 == 0")
+        table, rank, world, max_payload = push
+        with _on_device(x.device):
+            stream = _current_stream(qweight.device)
+            if splits is None:
+                splits = _pick_splits(x.device, N, K)
+            ws = _workspace(lib, x.device, stream, M, N, splits) if splits > 1 else None
+            rc = lib.ap_matmul_kbit_push(x2.data_ptr(), qweight.data_ptr(), plane_stride, lut.data_ptr(), M, N, K, w_bits,
+                                         splits if ws is not None else 1, ws.data_ptr() if ws is not None else None,
+                                         ws.numel() if ws is not None else 0, table, rank, world, max_payload, stream)
+        if rc != 0:
+            _raise(lib, rc, "matmul_kbit")
+        return None
     n_out = N // 2 if gated else N
     if gated and (N % 16 or M > 8):
         raise ValueError("gated=True needs a row count that is a multiple of 16 and at most eight activation rows")

@@ -39,6 +39,8 @@ def _lib():
     lib.ap_allreduce_oneshot.argtypes = [vp, vp, i, ctypes.POINTER(vp), i, i, sz, vp, vp]
     lib.ap_allreduce_residual_blocks.restype = i
     lib.ap_allreduce_residual_blocks.argtypes = [i, i]
+    lib.ap_allreduce_oneshot_collect.restype = i
+    lib.ap_allreduce_oneshot_collect.argtypes = [vp, i, i, vp, vp, vp, ctypes.POINTER(vp), i, i, sz, vp, vp]
     lib.ap_allreduce_oneshot_residual.restype = i
     lib.ap_allreduce_oneshot_residual.argtypes = [vp, vp, i, i, vp, vp, vp, ctypes.POINTER(vp), i, i, sz, vp, vp]
     lib._comm_ready = True
@@ -132,6 +134,37 @@ class OneShotAllReduce:
                                                         self.max_payload, self.status.data_ptr(),
                                                         torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "ap_allreduce_oneshot_residual")
+        return out
+
+    @property
+    def push_target(self):
+        """``(peer table, rank, world, max payload)``: what ``matmul_kbit(push=)`` needs to store a row-parallel
+        product straight into the ranks' inboxes (``ap_matmul_kbit_push``); ``collect`` must follow."""
+        return self._table, self.rank, self.world, self.max_payload
+
+    def collect(self, out: torch.Tensor, h: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
+                ssq: torch.Tensor | None = None) -> torch.Tensor:
+        """The second half of an all-reduce whose partial results ``matmul_kbit(push=)`` has stored in the
+        inboxes: ``out [rows, N]`` = the sum over the ranks, or, with ``h``, what ``residual`` leaves (``h``
+        updated in place, ``out = h * norm_weight``, ``ssq``)."""
+        if out.dim() != 2 or out.dtype != torch.float16 or not out.is_contiguous() or out.device != self.device:
+            raise TypeError("collect needs a contiguous float16 [rows, N] tensor on the buffers' device")
+        rows, n = out.shape
+        if h is not None:
+            for t in (h, norm_weight):
+                if t is None or t.dtype != torch.float16 or not t.is_contiguous() or t.device != self.device:
+                    raise TypeError("collect: h and norm_weight must be contiguous float16 tensors on the buffers' device")
+            blocks = self.residual_blocks(rows, n)
+            if h.shape != out.shape or norm_weight.numel() != n or blocks == 0 or ssq is None or \
+                    ssq.dtype != torch.float32 or ssq.numel() < rows * blocks or ssq.device != self.device:
+                raise ValueError("collect: h as out, norm_weight [N], ssq fp32 with rows * residual_blocks entries")
+        with torch.cuda.device(self.device):
+            rc = self.lib.ap_allreduce_oneshot_collect(out.data_ptr(), rows, n, h.data_ptr() if h is not None else None,
+                                                       norm_weight.data_ptr() if h is not None else None,
+                                                       ssq.data_ptr() if h is not None else None, self._table, self.rank,
+                                                       self.world, self.max_payload, self.status.data_ptr(),
+                                                       torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "ap_allreduce_oneshot_collect")
         return out
 
     def wait_expired(self) -> bool:

@@ -375,7 +375,7 @@ class AnyPrecisionLlama:
         that sums a row-parallel output): at most eight sequences, shapes the decode kernel takes."""
         if self.batch > 8:
             return False
-        if self.tp_world > 1 and (self.allreduce is None or not hasattr(self.allreduce, "residual") or
+        if self.tp_world > 1 and (self.allreduce is None or not hasattr(self.allreduce, "collect") or
                                   self.allreduce.residual_blocks(self.batch, self.spec.hidden) == 0):
             return False                                   # the process group's all-reduce has no folded form
         return all(m.bias is None and m.in_features % 128 == 0 and m.out_features % 16 == 0
@@ -393,8 +393,9 @@ class AnyPrecisionLlama:
         blocks = self.allreduce.residual_blocks(self.batch, s.hidden) if tp else None   # partial sums per row in ssq
 
         def add_and_scale(layer, x, norm_weight):
-            if tp:                                           # this rank's partial product, summed and added by the all-reduce
-                self.allreduce.residual(layer(x), h, norm_weight, ssq, out=y)
+            if tp:                                           # this rank's partial product goes from the kernel's epilogue into
+                layer.forward_push(x, self.allreduce)       # every rank's inbox; the collect sums and adds
+                self.allreduce.collect(y, h, norm_weight, ssq)
             else:
                 layer.forward_residual(x, h, norm_weight, ssq, out=y)
 

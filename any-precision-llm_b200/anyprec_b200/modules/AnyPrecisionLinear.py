@@ -203,6 +203,12 @@ class AnyPrecisionLinear(nn.Module):
         w_bits, lut = self._decode_operands(x, kwargs)
         return _ext.matmul_kbit(x, self.qweight, lut, w_bits, out=out, residual=(h, norm_weight, ssq))
 
+    def forward_push(self, x, allreduce, **kwargs):
+        """This rank's partial product of a row-parallel layer, stored by the kernel straight into the all-reduce
+        inboxes of all ranks (``comm.OneShotAllReduce``); ``allreduce.collect(...)`` then sums."""
+        w_bits, lut = self._decode_operands(x, kwargs)
+        return _ext.matmul_kbit(x, self.qweight, lut, w_bits, push=allreduce.push_target)
+
     def forward_prenorm(self, x, ssq, width, eps, out=None, blocks=None, **kwargs):
         """``self(rmsnorm-scaled x)`` for the ``x`` and ``ssq`` that ``forward_residual`` of the previous layer
         left (``width`` = that layer's ``out_features``); with a ``fuse_gated`` module the result is

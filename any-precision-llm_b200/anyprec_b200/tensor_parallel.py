@@ -20,6 +20,8 @@ from __future__ import annotations
 import dataclasses
 
 import torch
+
+import any_precision_ext as _ext
 import torch.distributed as dist
 
 from . import packing
@@ -72,9 +74,19 @@ def shard_forward(x: torch.Tensor, shard: LinearShard, w_bits: int, matmul, grou
     """One sharded layer.  ``x`` is the full activation for a column-parallel shard and the rank's
     feature slice for a row-parallel shard; the row-parallel result is all-reduced in place, by
     ``allreduce`` (e.g. a ``comm.OneShotAllReduce``) if given, else by the process group's."""
+    rows = x.numel() // x.shape[-1]
+    sharded_row = shard.style == "row" and dist.is_initialized() and dist.get_world_size(group) > 1
+    if sharded_row and allreduce is not None and hasattr(allreduce, "push_target") and rows <= 8 and \
+            _ext.gated_supported(x, shard.qweight, shard.luts[w_bits]) and matmul is _ext.matmul_kbit:
+        # the decode kernel stores its tiles straight into the ranks' inboxes; the collecting half sums
+        matmul(x, shard.qweight, shard.luts[w_bits], w_bits, push=allreduce.push_target)
+        if out is None:
+            out = torch.empty((*x.shape[:-1], shard.qweight.shape[1]), dtype=torch.float16, device=x.device)
+        allreduce.collect(out.view(rows, -1))
+        return out
     y = matmul(x, shard.qweight, shard.luts[w_bits], w_bits, out=out) if out is not None else \
         matmul(x, shard.qweight, shard.luts[w_bits], w_bits)
-    if shard.style == "row" and dist.is_initialized() and dist.get_world_size(group) > 1:
+    if sharded_row:
         if allreduce is not None:
             allreduce(y)
         else:

@@ -144,6 +144,28 @@ extern "C" int ap_matmul_kbit_prenorm(const void* x, const void* qweight, int64_
     return matmul_impl(x, qweight, plane_stride, lut, out, M, N, K, w_bits, splits, workspace, workspace_bytes, stream, &epi);
 }
 
+extern "C" int ap_matmul_kbit_push(const void* x, const void* qweight, int64_t plane_stride, const void* lut, int M, int N,
+                                   int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
+                                   void* const* peer_buffers, int rank, int world, size_t max_payload_bytes, void* stream) {
+    if (!peer_buffers) return AP_ERR_NULL_POINTER;
+    if (splits < 1 || world < 1 || world > ap::kCommMaxWorld || rank < 0 || rank >= world) return AP_ERR_BAD_SHAPE;
+    if (N % 16 != 0 || M > 8) return AP_ERR_UNSUPPORTED;
+    const size_t cap = (max_payload_bytes + 255) & ~static_cast<size_t>(255);
+    if (static_cast<size_t>(M) * N * 2 > cap) return AP_ERR_BAD_SHAPE;
+    ap::GemvEpilogue epi = {};
+    epi.mode = 5;
+    for (int p = 0; p < world; p++) {
+        if (!peer_buffers[p] || (reinterpret_cast<uintptr_t>(peer_buffers[p]) & 255)) return AP_ERR_BAD_ALIGNMENT;
+        epi.peer[p] = static_cast<unsigned char*>(peer_buffers[p]);
+    }
+    epi.rank = rank;
+    epi.world = world;
+    epi.cap = cap;
+    // `out` is not written in this mode; the checks want a non-null, even address
+    return matmul_impl(x, qweight, plane_stride, lut, peer_buffers[rank], M, N, K, w_bits, splits, workspace, workspace_bytes, stream,
+                       &epi);
+}
+
 extern "C" int ap_matmul_kbit_residual(const void* x, const void* qweight, int64_t plane_stride, const void* lut, void* out,
                                        int M, int N, int K, int w_bits, int splits, void* workspace, size_t workspace_bytes,
                                        void* resid, const void* norm_weight, void* ssq_out, void* stream) {

@@ -41,6 +41,7 @@
 #include <cstring>
 
 #include "anyprec_b200.h"
+#include "ap_kernels.h"
 
 namespace {
 
@@ -50,6 +51,7 @@ constexpr int kThreads = 256;
 constexpr size_t kSeqBytes = 4096;
 constexpr size_t kFlagBytes = (size_t)kMaxWorld * kMaxBlocks * sizeof(uint32_t) * 8;   // padded: 32 B per flag
 constexpr size_t kHeaderBytes = kSeqBytes + kFlagBytes;
+static_assert(kHeaderBytes == ap::kCommHeaderBytes && kMaxWorld == ap::kCommMaxWorld, "the decode kernel's push epilogue uses this layout");
 constexpr uint32_t kSpinLimit = 1u << 21;                  // polls of a thread's lines before it gives up (seconds)
 constexpr int kVecPerBlock = kThreads;                     // payload vectors (16 bytes) per block: one per thread
 
@@ -84,7 +86,9 @@ __device__ __forceinline__ uint32_t f2h(float a, float b) {
 // vectors, and step 4 becomes resid += fp16(sum) in place, out = new resid * norm_w (not yet divided by the root
 // mean square), ssq_out[row][block of the row] = sum of squares of the new resid in the block's range: what
 // ap_matmul_kbit_prenorm takes.  All ranks compute the same bits, so the replicated residual streams stay equal.
-template <bool RES>
+// PUSH false: the partial results are in the inboxes already (the decode kernel's epilogue stored them there,
+// ap_matmul_kbit_push); this launch only collects.
+template <bool RES, bool PUSH>
 __global__ void __launch_bounds__(kThreads)
 allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* __restrict__ out, int n_vec, int rank,
                          int world, size_t cap, int* __restrict__ status, int row_vec, int blocks_per_row,
@@ -130,12 +134,14 @@ allreduce_oneshot_kernel(PeerTable peers, const uint4* __restrict__ src, uint4* 
         }
     };
     // 1. push: this thread's vectors, to every rank
-    for (int v = v0 + threadIdx.x; v < v1; v += kThreads) {
-        const uint4 val = src[v];
-        for (int p = 0; p < world; p++) {
-            uint4* line = inbox_slot(peers.buf[p], gen, rank, cap) + 2 * (size_t)v;
-            st_line(line, val.x, val.y, seq);
-            st_line(line + 1, val.z, val.w, seq);
+    if constexpr (PUSH) {
+        for (int v = v0 + threadIdx.x; v < v1; v += kThreads) {
+            const uint4 val = src[v];
+            for (int p = 0; p < world; p++) {
+                uint4* line = inbox_slot(peers.buf[p], gen, rank, cap) + 2 * (size_t)v;
+                st_line(line, val.x, val.y, seq);
+                st_line(line + 1, val.z, val.w, seq);
+            }
         }
     }
     // 2. poll the same vectors' lines from every rank, add in rank order
@@ -271,7 +277,8 @@ namespace {
 
 int allreduce_impl(const void* src, void* out, int count, void* const* peer_buffers, int rank, int world,
                    size_t max_payload_bytes, int* status, void* stream, int rows, void* resid, const void* norm_weight,
-                   void* ssq_out) {
+                   void* ssq_out, bool pushed = false) {
+    if (pushed) src = out;                                   // not read
     if (!src || !out || !peer_buffers) return AP_ERR_NULL_POINTER;
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || count < 8 || count % 8) return AP_ERR_BAD_SHAPE;
     const size_t cap = (max_payload_bytes + 255) & ~static_cast<size_t>(255);
@@ -307,14 +314,16 @@ int allreduce_impl(const void* src, void* out, int count, void* const* peer_buff
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = resid ? cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<true>, t, static_cast<const uint4*>(src),
-                                               static_cast<uint4*>(out), n_vec, rank, world, cap, status, row_vec, bpr,
-                                               static_cast<uint4*>(resid), static_cast<const uint4*>(norm_weight),
-                                               static_cast<float*>(ssq_out))
-                          : cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<false>, t, static_cast<const uint4*>(src),
-                                               static_cast<uint4*>(out), n_vec, rank, world, cap, status, 0, 0,
-                                               static_cast<uint4*>(nullptr), static_cast<const uint4*>(nullptr),
-                                               static_cast<float*>(nullptr));
+    const uint4* sp = static_cast<const uint4*>(src);
+    uint4* op = static_cast<uint4*>(out);
+    uint4* rp = static_cast<uint4*>(resid);
+    const uint4* wp = static_cast<const uint4*>(norm_weight);
+    float* qp = static_cast<float*>(ssq_out);
+    cudaError_t e;
+    if (resid && !pushed) e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<true, true>, t, sp, op, n_vec, rank, world, cap, status, row_vec, bpr, rp, wp, qp);
+    else if (resid) e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<true, false>, t, sp, op, n_vec, rank, world, cap, status, row_vec, bpr, rp, wp, qp);
+    else if (!pushed) e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<false, true>, t, sp, op, n_vec, rank, world, cap, status, 0, 0, rp, wp, qp);
+    else e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<false, false>, t, sp, op, n_vec, rank, world, cap, status, 0, 0, rp, wp, qp);
     return e == cudaSuccess ? AP_OK : comm_fail(e);
 }
 
@@ -330,6 +339,14 @@ extern "C" int ap_allreduce_oneshot(const void* src, void* out, int count, void*
                                     size_t max_payload_bytes, int* status, void* stream) {
     return allreduce_impl(src, out, count, peer_buffers, rank, world, max_payload_bytes, status, stream, 0, nullptr, nullptr,
                           nullptr);
+}
+
+extern "C" int ap_allreduce_oneshot_collect(void* out, int rows, int row_len, void* resid, const void* norm_weight,
+                                            void* ssq_out, void* const* peer_buffers, int rank, int world,
+                                            size_t max_payload_bytes, int* status, void* stream) {
+    if (rows < 1 || row_len < 8) return AP_ERR_BAD_SHAPE;
+    return allreduce_impl(nullptr, out, rows * row_len, peer_buffers, rank, world, max_payload_bytes, status, stream, rows, resid,
+                          norm_weight, ssq_out, true);
 }
 
 extern "C" int ap_allreduce_oneshot_residual(const void* src, void* out, int rows, int row_len, void* resid,

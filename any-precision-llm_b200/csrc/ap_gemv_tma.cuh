@@ -122,9 +122,12 @@ __device__ __forceinline__ void dec_row_scale(const GemvEpilogue& epi, int m, in
 //         square: the products are scaled by rn_s[m] = rsqrt(mean square + eps) first (a matrix product commutes
 //         with a scale per batch row);
 //   4     residual update: resid[m][row] += fp16(product), and the output is the new residual times the next
-//         norm's weight, with this tile's sum of squares of the new residual in ssq_out[m][tile].
+//         norm's weight, with this tile's sum of squares of the new residual in ssq_out[m][tile];
+//   5     the tile goes to the all-reduce inboxes of all ranks (tensor parallelism: a row-parallel layer's
+//         partial result), nothing is stored locally.
 __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const float* red, const float* partials, int S, int M, int N,
-                                          int row0, __half* out, int tid, const float* rn_s, float pre_h, float pre_w) {
+                                          int row0, __half* out, int tid, const float* rn_s, float pre_h, float pre_w,
+                                          uint32_t pre_seq) {
     constexpr int kThreads = kGemvMaxWarps * 32;
     auto total = [&](int m, int r) {
         float sum = 0.f;
@@ -150,6 +153,19 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
         for (int i = tid; i < 16 * M; i += kThreads) {
             const int m = i >> 4, r = i & 15;
             out[(size_t)m * N + row0 + r] = __float2half_rn(total(m, r) * rn_s[m]);
+        }
+    } else if (mode == 5) {
+        // Two neighbouring rows' fp16 sums and the call's number make one 8-byte store, which arrives whole; element
+        // e of the [M][N] result lives at byte (e / 2) * 8 of the sender's slot in the call's generation.
+        const uint32_t seq = pre_seq + 1u;
+        const unsigned long long slot = kCommHeaderBytes + ((unsigned long long)(seq & 1u) * kCommMaxWorld + epi.rank) * 2ull * epi.cap;
+        for (int i = tid; i < 8 * M; i += kThreads) {
+            const int m = i >> 3, r = 2 * (i & 7);
+            const __half2 v = __floats2half2_rn(total(m, r), total(m, r + 1));
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(&v);
+            const unsigned long long at = slot + (((unsigned long long)m * N + row0 + r) >> 1) * 8ull;
+            for (int p = 0; p < epi.world; p++)
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(epi.peer[p] + at), "r"(word), "r"(seq) : "memory");
         }
     } else if (tid < 128) {                                  // mode 4; four whole warps: 16 lanes per batch row
         const int m = tid >> 4, r = tid & 15;
@@ -468,11 +484,15 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     // Mode 4 of the decoder variants: this thread's old residual and norm weight, requested before the reduction
     // below so that their round trip hides behind it.
     float pre_h = 0.f, pre_w = 0.f;
+    uint32_t pre_seq = 0u;
     if constexpr (DEC) {
         if (epi.mode == 4 && tid < 16 * M) {
             pre_h = __half2float(epi.resid[(size_t)(tid >> 4) * N + row0 + (tid & 15)]);
             pre_w = __half2float(epi.norm_w[row0 + (tid & 15)]);
         }
+        // mode 5: the number of all-reduce calls completed so far, from this rank's communication buffer (written
+        // by the previous call's last block, which this launch's dependency wait has seen end)
+        if (epi.mode == 5) pre_seq = __ldcg(reinterpret_cast<const uint32_t*>(epi.peer[epi.rank]));
     }
     // Combine the warps' partial tiles: acc = {(g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)}.
     float* mine = red + warp * 128;
@@ -485,7 +505,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     // decoder's variants (DEC) hand them to dec_epilogue.
     if (gridDim.y == 1) {
         if constexpr (DEC) {
-            dec_epilogue(epi, red, nullptr, 0, M, N, row0, out, tid, rn_s, pre_h, pre_w);
+            dec_epilogue(epi, red, nullptr, 0, M, N, row0, out, tid, rn_s, pre_h, pre_w, pre_seq);
         } else {
             for (int i = tid; i < 16 * M; i += kThreads) {
                 const int m = i >> 4, r = i & 15;            // 16 consecutive rows per m: 32-byte stores
@@ -514,7 +534,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
         if (*flag) {
             __threadfence();
             if constexpr (DEC) {
-                dec_epilogue(epi, nullptr, partials, S, M, N, row0, out, tid, rn_s, pre_h, pre_w);
+                dec_epilogue(epi, nullptr, partials, S, M, N, row0, out, tid, rn_s, pre_h, pre_w, pre_seq);
             } else {
                 for (int i = tid; i < 16 * M; i += kThreads) {
                     const int m = i >> 4, r = i & 15;

@@ -10,7 +10,12 @@ namespace ap {
 // gemv_kbit_tma_kernel): mode 1 gated (silu(gate) * up of stacked rows), 2 scaled by the per-row
 // rsqrt(mean square + eps) taken from `ssq_in` ([M][ssq_blocks] partial sums of squares, mean over
 // 1 / inv_width values), 3 both, 4 residual update (`resid` [M][N] += product; out = new residual *
-// `norm_w`; `ssq_out` [M][N / 16] partial sums of squares of the new residual).
+// `norm_w`; `ssq_out` [M][N / 16] partial sums of squares of the new residual), 5 push to the peers' inboxes.
+// Layout of a rank's communication buffer (ap_comm.cu): header, then inbox[2 generations][kCommMaxWorld senders]
+// [2 * cap bytes]; sixteen-byte lines {word, seq, word, seq}.
+constexpr int kCommMaxWorld = 8;
+constexpr unsigned long long kCommHeaderBytes = 20480;
+
 struct GemvEpilogue {
     int mode;
     const float* ssq_in;
@@ -20,6 +25,12 @@ struct GemvEpilogue {
     __half* resid;
     const __half* norm_w;
     float* ssq_out;
+    // mode 5: the product is a row-parallel layer's partial result; instead of storing it, the tile is pushed
+    // into slot `rank` of the all-reduce inbox of every rank (the first step of ap_allreduce_oneshot, done
+    // from here; ap_allreduce_oneshot_collect does the rest)
+    unsigned char* peer[kCommMaxWorld];
+    int rank, world;
+    unsigned long long cap;
 };
 
 // All launchers enqueue on `stream`, never synchronise, never allocate, and return the

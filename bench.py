@@ -693,10 +693,17 @@ def tensor_parallel_figures(args, rank, world, device, layers, full):
         if tp_check != "ok":
             raise SystemExit(f"tp_check failed on {name}: the all-reduced row-parallel output differs from the sum of the partials")
 
+    push_ok = allreduce is not None and hasattr(allreduce, "push_target") and os.environ.get("AP_TP_PUSH", "1") != "0"
+
     def one_pass(w, m, do_gemv=True, do_reduce=True):
         for name, sh in shards:
             xin = (x_full if sh.style == "col" else bufs[("in", sh.in_features)])[:m]
             out = bufs[(sh.style, sh.out_features)][:m]
+            if do_gemv and do_reduce and sh.style == "row" and world > 1 and push_ok and m <= 8:
+                # the product stores its tiles straight into every rank's inbox; the collecting half sums
+                ext.matmul_kbit(xin, sh.qweight, sh.luts[w], w, push=allreduce.push_target)
+                allreduce.collect(out)
+                continue
             if do_gemv:
                 ext.matmul_kbit(xin, sh.qweight, sh.luts[w], w, out=out)
             if do_reduce and sh.style == "row" and world > 1:
@@ -777,12 +784,15 @@ def tensor_parallel_figures(args, rank, world, device, layers, full):
         red_ms = timed(lambda: [one_pass(w, M, do_gemv=False) for w in W_BITS], short, 3)
         breakdown = {"gemv_only_ms_per_step": round(gemv_ms, 4), "allreduce_only_ms_per_step": round(red_ms, 4),
                      "both_ms_per_step": round(ms_per_step, 4),
-                     "note": "the same step captured without the all-reduces and without the GEMVs"}
+                     "note": "the same step captured without the all-reduces and without the GEMVs (there every "
+                             "all-reduce is the one-kernel form; in the timed step the row-parallel products store "
+                             "their tiles into the ranks' inboxes themselves and the all-reduce only collects)"}
 
     launches = len(shards) * len(W_BITS)
     config = {"workload": f"llama2-70b linear-layer set x{layers} layers, tensor-parallel tp{world} "
                           f"(q/k/v/gate/up on N, o/down on K + all-reduce), matmul_kbit M={M}, w_bits 3..8 sweep",
-              "allreduce": allreduce_kind, "tp_check": tp_check,
+              "allreduce": allreduce_kind + (" fed by the products' epilogues (ap_matmul_kbit_push + ap_allreduce_oneshot_collect)"
+                                             if push_ok else ""), "tp_check": tp_check,
               "fused_layers": "q+k+v and gate+up stacked by rows (one launch each)" if fuse else "none",
               "batch": M, "parallelism": f"tp{world}", "launches_per_step_per_rank": launches,
               "allreduces_per_step": (2 * layers * len(W_BITS)) if world > 1 else 0, "bytes_per_step": bytes_per_step,

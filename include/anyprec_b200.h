@@ -220,7 +220,20 @@ int ap_gemm_kbit_splitk(const void* x, const void* qweight, int64_t plane_stride
  *     resid over the blocks' ranges: the x, ssq and ssq_blocks of ap_matmul_kbit_prenorm (width = row_len).
  *     Counts as one call of the sequence above.  ap_allreduce_residual_blocks returns 0 where the shape is not
  *     supported (rows * blocks above 64).
+ *   ap_matmul_kbit_push + ap_allreduce_oneshot_collect
+ *     the all-reduce of a row-parallel product with its first step done by the product itself: the decode kernel's
+ *     epilogue stores every finished tile straight into the inboxes of all ranks (no local result), and the collect
+ *     call polls, sums in rank order and, with `resid` given, does what ap_allreduce_oneshot_residual does after its
+ *     sum (resid NULL: out = the sum).  The pair counts as one call of the sequence; every rank must use the pair (or
+ *     the one-kernel form) for the same call.  ap_matmul_kbit_push: operands and limits as ap_matmul_kbit_gated
+ *     (M <= 8, N % 16 == 0, fast-kernel operands), M * N * 2 <= max_payload_bytes.
  */
+int ap_matmul_kbit_push(const void* x, const void* qweight, int64_t plane_stride, const void* lut, int M, int N, int K,
+                        int w_bits, int splits, void* workspace, size_t workspace_bytes, void* const* peer_buffers,
+                        int rank, int world, size_t max_payload_bytes, void* stream);
+int ap_allreduce_oneshot_collect(void* out, int rows, int row_len, void* resid, const void* norm_weight, void* ssq_out,
+                                 void* const* peer_buffers, int rank, int world, size_t max_payload_bytes, int* status,
+                                 void* stream);
 int ap_allreduce_residual_blocks(int rows, int row_len);
 int ap_allreduce_oneshot_residual(const void* src, void* out, int rows, int row_len, void* resid, const void* norm_weight,
                                   void* ssq_out, void* const* peer_buffers, int rank, int world, size_t max_payload_bytes,

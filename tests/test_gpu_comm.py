@@ -63,6 +63,31 @@ def test_single_rank_roundtrip_and_graph_replay():
         assert torch.equal(h, want_h) and torch.equal(out, (want_h.float() * gw.float()).half())
         assert torch.allclose(ssq.sum(-1), want_h.float().pow(2).sum(-1), rtol=1e-5)
     assert ar.residual_blocks(8, 32768) == 0              # 8 rows x 16 blocks: more blocks than a call may have
+    # the product that stores its tiles into the inboxes itself, then the collecting half (plain and residual
+    # form), unsplit and split along K, between ordinary calls
+    import any_precision_ext as ext
+    from anyprec_b200 import packing
+    N, K = 512, 2048
+    q = packing.random_qweight(8, N, K, device=dev, generator=gen)
+    for w in (3, 4, 6, 8):
+        lut = packing.random_lut(N, w, device=dev, generator=gen)
+        for rows in (1, 3, 8):
+            x = torch.randn((rows, K), device=dev, generator=gen).half()
+            for splits in (1, 2):
+                want = ext.matmul_kbit(x, q, lut, w, splits=splits)
+                assert ext.matmul_kbit(x, q, lut, w, splits=splits, push=ar.push_target) is None
+                got = ar.collect(torch.empty_like(want))
+                assert torch.equal(got, want), (w, rows, splits)
+                ar(torch.ones(8, device=dev, dtype=torch.float16))
+                h0 = torch.randn((rows, N), device=dev, generator=gen).half()
+                gw = (1 + 0.1 * torch.randn(N, device=dev, generator=gen)).half()
+                h, y = h0.clone(), torch.empty_like(want)
+                ssq = torch.zeros((rows, ar.residual_blocks(rows, N)), device=dev)
+                ext.matmul_kbit(x, q, lut, w, splits=splits, push=ar.push_target)
+                ar.collect(y, h, gw, ssq)
+                want_h = (h0.float() + want.float()).half()
+                assert torch.equal(h, want_h) and torch.equal(y, (want_h.float() * gw.float()).half())
+                assert torch.allclose(ssq.sum(-1), want_h.float().pow(2).sum(-1), rtol=1e-5)
     assert not ar.wait_expired()
     ar.close()
 
@@ -142,6 +167,21 @@ def _rank_main(rank, world, port, result):
         torch.cuda.synchronize()
         ok = ok and torch.equal(h.cpu(), want_h) and torch.equal(out.cpu(), (want_h.float() * gw.float()).half())
         ok = ok and torch.allclose(ssq.sum(-1).cpu(), want_h.float().pow(2).sum(-1), rtol=1e-5)
+        # every rank's product pushed from the kernel's epilogue, collected into the same bits as the one-kernel form
+        import any_precision_ext as ext
+        from anyprec_b200 import packing
+        g = torch.Generator(device=dev).manual_seed(50 + rank)
+        Nn, Kk = 1024, 1024
+        q = packing.random_qweight(8, Nn, Kk, device=dev, generator=g)
+        lut = packing.random_lut(Nn, 4, device=dev, generator=g)
+        for rows_ in (1, 8):
+            xr = torch.randn((rows_, Kk), device=dev, generator=g).half()
+            part = ext.matmul_kbit(xr, q, lut, 4)
+            want2 = ar(part.clone())
+            ext.matmul_kbit(xr, q, lut, 4, push=ar.push_target)
+            got2 = ar.collect(torch.empty_like(part))
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(got2, want2)
         ok = ok and not ar.wait_expired()
         ar.close()
         result[rank] = ok
