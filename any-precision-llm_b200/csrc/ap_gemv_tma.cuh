@@ -125,6 +125,7 @@ __device__ __forceinline__ void dec_row_scale(const GemvEpilogue& epi, int m, in
 //         norm's weight, with this tile's sum of squares of the new residual in ssq_out[m][tile];
 //   5     the tile goes to the all-reduce inboxes of all ranks (tensor parallelism: a row-parallel layer's
 //         partial result), nothing is stored locally.
+template <int DEC>
 __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const float* red, const float* partials, int S, int M, int N,
                                           int row0, __half* out, int tid, const float* rn_s, float pre_h, float pre_w,
                                           uint32_t pre_seq) {
@@ -139,6 +140,21 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
         }
         return sum;
     };
+    if constexpr (DEC == 2) {
+        // Two neighbouring rows' fp16 sums and the call's number make one 8-byte store, which arrives whole; element
+        // e of the [M][N] result lives at byte (e / 2) * 8 of the sender's slot in the call's generation.
+        const uint32_t seq = pre_seq + 1u;
+        const unsigned long long slot = kCommHeaderBytes + ((unsigned long long)(seq & 1u) * kCommMaxWorld + epi.rank) * 2ull * epi.cap;
+        for (int i = tid; i < 8 * M; i += kThreads) {
+            const int m = i >> 3, r = 2 * (i & 7);
+            const __half2 v = __floats2half2_rn(total(m, r), total(m, r + 1));
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(&v);
+            const unsigned long long at = slot + (((unsigned long long)m * N + row0 + r) >> 1) * 8ull;
+            for (int p = 0; p < epi.world; p++)
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(epi.peer[p] + at), "r"(word), "r"(seq) : "memory");
+        }
+        return;
+    }
     const int mode = epi.mode;
     if (mode == 1 || mode == 3) {
         for (int i = tid; i < 8 * M; i += kThreads) {
@@ -153,19 +169,6 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
         for (int i = tid; i < 16 * M; i += kThreads) {
             const int m = i >> 4, r = i & 15;
             out[(size_t)m * N + row0 + r] = __float2half_rn(total(m, r) * rn_s[m]);
-        }
-    } else if (mode == 5) {
-        // Two neighbouring rows' fp16 sums and the call's number make one 8-byte store, which arrives whole; element
-        // e of the [M][N] result lives at byte (e / 2) * 8 of the sender's slot in the call's generation.
-        const uint32_t seq = pre_seq + 1u;
-        const unsigned long long slot = kCommHeaderBytes + ((unsigned long long)(seq & 1u) * kCommMaxWorld + epi.rank) * 2ull * epi.cap;
-        for (int i = tid; i < 8 * M; i += kThreads) {
-            const int m = i >> 3, r = 2 * (i & 7);
-            const __half2 v = __floats2half2_rn(total(m, r), total(m, r + 1));
-            const uint32_t word = *reinterpret_cast<const uint32_t*>(&v);
-            const unsigned long long at = slot + (((unsigned long long)m * N + row0 + r) >> 1) * 8ull;
-            for (int p = 0; p < epi.world; p++)
-                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(epi.peer[p] + at), "r"(word), "r"(seq) : "memory");
         }
     } else if (tid < 128) {                                  // mode 4; four whole warps: 16 lanes per batch row
         const int m = tid >> 4, r = tid & 15;
@@ -185,7 +188,7 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
     }
 }
 
-template <int W, int OCC, int MODE, bool DEC = false>
+template <int W, int OCC, int MODE, int DEC = 0>
 __global__ void __launch_bounds__(kGemvMaxWarps * 32, OCC)
 gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __restrict__ x,
                      const uint16_t* __restrict__ lut, __half* __restrict__ out, int M, int N, int K, int mpad,
@@ -382,7 +385,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     if (warp == 0) {
         for (int i = 0; i < first; i++) request_x(i);
     }
-    if constexpr (DEC) {
+    if constexpr (DEC == 1) {
         // by the warps that do not issue the copies, while the first chunks travel
         if ((epi.mode == 2 || epi.mode == 3) && kGemvMaxWarps - 1 - warp < M) dec_row_scale(epi, kGemvMaxWarps - 1 - warp, lane, rn_s);
     }
@@ -485,15 +488,15 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     // below so that their round trip hides behind it.
     float pre_h = 0.f, pre_w = 0.f;
     uint32_t pre_seq = 0u;
-    if constexpr (DEC) {
+    if constexpr (DEC == 1) {
         if (epi.mode == 4 && tid < 16 * M) {
             pre_h = __half2float(epi.resid[(size_t)(tid >> 4) * N + row0 + (tid & 15)]);
             pre_w = __half2float(epi.norm_w[row0 + (tid & 15)]);
         }
-        // mode 5: the number of all-reduce calls completed so far, from this rank's communication buffer (written
-        // by the previous call's last block, which this launch's dependency wait has seen end)
-        if (epi.mode == 5) pre_seq = __ldcg(reinterpret_cast<const uint32_t*>(epi.peer[epi.rank]));
     }
+    // push variant: the number of all-reduce calls completed so far, from this rank's communication buffer (written
+    // by the previous call's last block, which this launch's dependency wait has seen end)
+    if constexpr (DEC == 2) pre_seq = __ldcg(reinterpret_cast<const uint32_t*>(epi.peer[epi.rank]));
     // Combine the warps' partial tiles: acc = {(g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)}.
     float* mine = red + warp * 128;
     mine[g * 8 + 2 * t] = acc[0][0] + acc[1][0];
@@ -505,7 +508,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     // decoder's variants (DEC) hand them to dec_epilogue.
     if (gridDim.y == 1) {
         if constexpr (DEC) {
-            dec_epilogue(epi, red, nullptr, 0, M, N, row0, out, tid, rn_s, pre_h, pre_w, pre_seq);
+            dec_epilogue<DEC>(epi, red, nullptr, 0, M, N, row0, out, tid, rn_s, pre_h, pre_w, pre_seq);
         } else {
             for (int i = tid; i < 16 * M; i += kThreads) {
                 const int m = i >> 4, r = i & 15;            // 16 consecutive rows per m: 32-byte stores
@@ -534,7 +537,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
         if (*flag) {
             __threadfence();
             if constexpr (DEC) {
-                dec_epilogue(epi, nullptr, partials, S, M, N, row0, out, tid, rn_s, pre_h, pre_w, pre_seq);
+                dec_epilogue<DEC>(epi, nullptr, partials, S, M, N, row0, out, tid, rn_s, pre_h, pre_w, pre_seq);
             } else {
                 for (int i = tid; i < 16 * M; i += kThreads) {
                     const int m = i >> 4, r = i & 15;
@@ -591,7 +594,7 @@ static bool encode_plane_map(CUtensorMap* map, const void* qweight, long long pl
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int W, int OCC, int MODE, bool DEC = false>
+template <int W, int OCC, int MODE, int DEC = 0>
 static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const uint16_t* lut, __half* out, int M, int N,
                                   int K, int splits, int split_chunks, float* partials, int* tickets, cudaStream_t stream,
                                   const GemvEpilogue& epi) {
@@ -649,8 +652,9 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
     if (M > 8 && splits > 1) { *used = false; return cudaSuccess; }              // the caller runs the passes one by one
     const bool many_blocks = (long long)(N / 16) * splits * ((M + 7) / 8) >= 3LL * sms;
 #define AP_TMA_GO(OCC_, MODE_) \
-    return epi ? launch_tma_occ<W, OCC_, MODE_, true>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi) \
-               : launch_tma_occ<W, OCC_, MODE_, false>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, plain)
+    return !epi ? launch_tma_occ<W, OCC_, MODE_, 0>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, plain) \
+         : epi->mode == 5 ? launch_tma_occ<W, OCC_, MODE_, 2>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi) \
+                          : launch_tma_occ<W, OCC_, MODE_, 1>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi)
     if constexpr (W == 3) {
         if (many_blocks) AP_TMA_GO(3, 2);
         AP_TMA_GO(2, 2);
