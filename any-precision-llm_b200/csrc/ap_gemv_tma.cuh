@@ -125,6 +125,9 @@ __device__ __forceinline__ void dec_row_scale(const GemvEpilogue& epi, int m, in
 //         norm's weight, with this tile's sum of squares of the new residual in ssq_out[m][tile];
 //   5     the tile goes to the all-reduce inboxes of all ranks (tensor parallelism: a row-parallel layer's
 //         partial result), nothing is stored locally.
+// The mode is the kernel's template argument DEC (0 = the plain kernel): one instantiation per mode, because the
+// main loop's machine code turned out to depend on what follows it (a common variant with the mode read at run
+// time ran the same loop 0.3-1.4 us per launch slower).
 template <int DEC>
 __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const float* red, const float* partials, int S, int M, int N,
                                           int row0, __half* out, int tid, const float* rn_s, float pre_h, float pre_w,
@@ -140,7 +143,7 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
         }
         return sum;
     };
-    if constexpr (DEC == 2) {
+    if constexpr (DEC == 5) {
         // Two neighbouring rows' fp16 sums and the call's number make one 8-byte store, which arrives whole; element
         // e of the [M][N] result lives at byte (e / 2) * 8 of the sender's slot in the call's generation.
         const uint32_t seq = pre_seq + 1u;
@@ -155,8 +158,8 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
         }
         return;
     }
-    const int mode = epi.mode;
-    if (mode == 1 || mode == 3) {
+    constexpr int mode = DEC;
+    if constexpr (mode == 1 || mode == 3) {
         for (int i = tid; i < 8 * M; i += kThreads) {
             const int m = i >> 3, r = i & 7;
             float gs = total(m, r), us = total(m, r + 8);
@@ -165,7 +168,7 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
             const float a = __half2float(__float2half_rn(gf / (1.f + __expf(-gf))));
             out[(size_t)m * (N >> 1) + (row0 >> 1) + r] = __float2half_rn(a * uf);
         }
-    } else if (mode == 2) {
+    } else if constexpr (mode == 2) {
         for (int i = tid; i < 16 * M; i += kThreads) {
             const int m = i >> 4, r = i & 15;
             out[(size_t)m * N + row0 + r] = __float2half_rn(total(m, r) * rn_s[m]);
@@ -385,9 +388,9 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     if (warp == 0) {
         for (int i = 0; i < first; i++) request_x(i);
     }
-    if constexpr (DEC == 1) {
+    if constexpr (DEC == 2 || DEC == 3) {
         // by the warps that do not issue the copies, while the first chunks travel
-        if ((epi.mode == 2 || epi.mode == 3) && kGemvMaxWarps - 1 - warp < M) dec_row_scale(epi, kGemvMaxWarps - 1 - warp, lane, rn_s);
+        if (kGemvMaxWarps - 1 - warp < M) dec_row_scale(epi, kGemvMaxWarps - 1 - warp, lane, rn_s);
     }
 
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -488,15 +491,15 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     // below so that their round trip hides behind it.
     float pre_h = 0.f, pre_w = 0.f;
     uint32_t pre_seq = 0u;
-    if constexpr (DEC == 1) {
-        if (epi.mode == 4 && tid < 16 * M) {
+    if constexpr (DEC == 4) {
+        if (tid < 16 * M) {
             pre_h = __half2float(epi.resid[(size_t)(tid >> 4) * N + row0 + (tid & 15)]);
             pre_w = __half2float(epi.norm_w[row0 + (tid & 15)]);
         }
     }
     // push variant: the number of all-reduce calls completed so far, from this rank's communication buffer (written
     // by the previous call's last block, which this launch's dependency wait has seen end)
-    if constexpr (DEC == 2) pre_seq = __ldcg(reinterpret_cast<const uint32_t*>(epi.peer[epi.rank]));
+    if constexpr (DEC == 5) pre_seq = __ldcg(reinterpret_cast<const uint32_t*>(epi.peer[epi.rank]));
     // Combine the warps' partial tiles: acc = {(g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)}.
     float* mine = red + warp * 128;
     mine[g * 8 + 2 * t] = acc[0][0] + acc[1][0];
@@ -652,9 +655,17 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
     if (M > 8 && splits > 1) { *used = false; return cudaSuccess; }              // the caller runs the passes one by one
     const bool many_blocks = (long long)(N / 16) * splits * ((M + 7) / 8) >= 3LL * sms;
 #define AP_TMA_GO(OCC_, MODE_) \
-    return !epi ? launch_tma_occ<W, OCC_, MODE_, 0>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, plain) \
-         : epi->mode == 5 ? launch_tma_occ<W, OCC_, MODE_, 2>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi) \
-                          : launch_tma_occ<W, OCC_, MODE_, 1>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi)
+    do {                                                                                                                         \
+        if (!epi) return launch_tma_occ<W, OCC_, MODE_, 0>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, plain); \
+        switch (epi->mode) {                                                                                                     \
+            case 1: return launch_tma_occ<W, OCC_, MODE_, 1>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi); \
+            case 2: return launch_tma_occ<W, OCC_, MODE_, 2>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi); \
+            case 3: return launch_tma_occ<W, OCC_, MODE_, 3>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi); \
+            case 4: return launch_tma_occ<W, OCC_, MODE_, 4>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi); \
+            case 5: return launch_tma_occ<W, OCC_, MODE_, 5>(map, x, lut, out, M, N, K, splits, split_chunks, partials, tickets, stream, *epi); \
+            default: return cudaErrorInvalidValue;                                                                               \
+        }                                                                                                                        \
+    } while (0)
     if constexpr (W == 3) {
         if (many_blocks) AP_TMA_GO(3, 2);
         AP_TMA_GO(2, 2);
