@@ -191,7 +191,7 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
     }
 }
 
-template <int W, int OCC, int MODE, int DEC = 0>
+template <int W, int OCC, int MODE, int DEC = 0, bool SPLIT = true>
 __global__ void __launch_bounds__(kGemvMaxWarps * 32, OCC)
 gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __restrict__ x,
                      const uint16_t* __restrict__ lut, __half* __restrict__ out, int M, int N, int K, int mpad,
@@ -243,21 +243,22 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     // two sets of four warps, and with an odd number of buffers so do the uses of one buffer; blocks
     // of planes may also land out of order.  Hence two barriers per buffer, taken in turn by its
     // uses: a barrier's phases are then all waited for by the same four warps, in order.
-    auto bar_of = [&](int i) { return bar_sh + 8u * (uint32_t)(2 * (i % nbuf) + ((i / nbuf) & 1)); };
-    // Request local chunk i (row chunk c_begin + i) into its buffer.  Called by a whole warp.
-    auto request_planes = [&](int i) {
-        const int b = i % nbuf;
+    // (buffer b = i % nbuf in its use number rnd = i / nbuf; the main loop carries b and rnd along instead of
+    // dividing)
+    auto bar_at = [&](int b, int rnd) { return bar_sh + 8u * (uint32_t)(2 * b + (rnd & 1)); };
+    // Request local chunk i (row chunk c_begin + i) into its buffer b in its use rnd.  Called by a whole warp.
+    auto request_planes = [&](int i, int b, int rnd) {
         if (lane == 0) {
-            const uint32_t bar = bar_of(i);
+            const uint32_t bar = bar_at(b, rnd);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)T::kPlaneBytes) : "memory");
             tensor_g2s_3d(bufs_sh + b * buf_bytes, &qmap, (c_begin + i) * kTmaChunkWords, row0, 0, bar);
         }
         __syncwarp();
     };
-    auto request_x = [&](int i) {
-        const int b = i % nbuf, c = c_begin + i;
+    auto request_x = [&](int i, int b, int rnd) {
+        const int c = c_begin + i;
         const uint32_t bytes = (uint32_t)chunk_words(c) * 64u;            // 32 weights per word, 2 bytes each
-        const uint32_t bar = bar_of(i);
+        const uint32_t bar = bar_at(b, rnd);
         if (lane == 0)
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)M) : "memory");
         __syncwarp();
@@ -301,7 +302,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     __syncthreads();                                         // barriers initialised
     const int first = nchunks < nbuf ? nchunks : nbuf;
     if (warp == 0) {
-        for (int i = 0; i < first; i++) request_planes(i);   // weights never depend on the previous kernel
+        for (int i = 0; i < first; i++) request_planes(i, i, 0);   // weights never depend on the previous kernel
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     AP_PROF(6);
@@ -386,7 +387,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     asm volatile("griddepcontrol.wait;" ::: "memory");
     AP_PROF(7);
     if (warp == 0) {
-        for (int i = 0; i < first; i++) request_x(i);
+        for (int i = 0; i < first; i++) request_x(i, i, 0);
     }
     if constexpr (DEC == 2 || DEC == 3) {
         // by the warps that do not issue the copies, while the first chunks travel
@@ -400,15 +401,17 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     const uint32_t row_a = (uint32_t)g * 128u, row_b = (uint32_t)(g + 8) * 128u;
     bool ok = true;
 
+    // this warp's steps are two chunks apart: its buffer index and the buffer's use number move along with it
+    int b = warp >> 2, rnd = 0;                              // nbuf >= 2, so chunk 0 or 1 is buffer 0 or 1, first use
     for (int s = warp; s < total_steps && ok; s += kGemvMaxWarps) {
-        const int i = s >> 2, sl = s & 3, b = i % nbuf;
+        const int i = s >> 2, sl = s & 3;
         const int cw_words = chunk_words(c_begin + i);
         const int wic = 8 * sl + 2 * t;                      // this lane's first word inside the chunk
         const bool valid = wic < cw_words;
         const uint32_t buf = bufs_sh + b * buf_bytes;
         // Every step waits for its chunk, even an empty one of a short last chunk: its "done" below
         // must not be counted while the buffer still holds an earlier chunk.
-        ok = mbar_wait_bounded(bar_of(i), (uint32_t)((i / nbuf) >> 1) & 1u);
+        ok = mbar_wait_bounded(bar_at(b, rnd), (uint32_t)(rnd >> 1) & 1u);
         if (s == warp) AP_PROF(2);
         if (ok && 8 * sl < cw_words) {                       // the step has at least one word (warp-uniform)
             const uint32_t piece = ((uint32_t)(2 * sl + (t >> 1)) ^ (uint32_t)(g & 7)) << 4;
@@ -476,13 +479,15 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
         if (lane == 0) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(empty) : "memory");
         const int inext = i + nbuf;
         if (sl == 0 && ok && inext < nchunks) {
-            ok = mbar_wait_bounded(empty, (uint32_t)(i / nbuf) & 1u);
+            ok = mbar_wait_bounded(empty, (uint32_t)rnd & 1u);
             if (ok) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                request_planes(inext);
-                request_x(inext);
+                request_planes(inext, b, rnd + 1);
+                request_x(inext, b, rnd + 1);
             }
         }
+        b += 2;                                              // kGemvMaxWarps / 4 chunks further
+        if (b >= nbuf) { b -= nbuf; rnd++; }
     }
     if (!ok && lane == 0) atomicExch(&ap_gemv_wait_expired, 1);
     AP_PROF(3);
@@ -509,7 +514,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     __syncthreads();
     // What becomes of a finished 16-row tile: plain kernels round the fp32 products to fp16 and store them; the
     // decoder's variants (DEC) hand them to dec_epilogue.
-    if (gridDim.y == 1) {
+    if (!SPLIT || gridDim.y == 1) {
         if constexpr (DEC) {
             dec_epilogue<DEC>(epi, red, nullptr, 0, M, N, row0, out, tid, rn_s, pre_h, pre_w, pre_seq);
         } else {
@@ -609,7 +614,9 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         int most = 0;
         for (int mp = 1; mp <= 8; mp *= 2) most = T::total(mp) > most ? T::total(mp) : most;
-        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
@@ -624,7 +631,10 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC>, map, x, lut, out, M, N, K, mpad, split_chunks,
+    if (splits <= 1)                                         // no K split: the instantiation without that epilogue
+        return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false>, map, x, lut, out, M, N, K, mpad,
+                                  split_chunks, partials, tickets, epi);
+    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true>, map, x, lut, out, M, N, K, mpad, split_chunks,
                               partials, tickets, epi);
 }
 
