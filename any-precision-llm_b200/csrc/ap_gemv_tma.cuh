@@ -191,16 +191,20 @@ __device__ __forceinline__ void dec_epilogue(const GemvEpilogue& epi, const floa
     }
 }
 
-template <int W, int OCC, int MODE, int DEC = 0, bool SPLIT = true>
+template <int W, int OCC, int MODE, int DEC = 0, bool SPLIT = true, bool ONE = false>
 __global__ void __launch_bounds__(kGemvMaxWarps * 32, OCC)
 gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __restrict__ x,
-                     const uint16_t* __restrict__ lut, __half* __restrict__ out, int M, int N, int K, int mpad,
+                     const uint16_t* __restrict__ lut, __half* __restrict__ out, int M_, int N, int K, int mpad_,
                      int split_chunks, float* __restrict__ partials, int* __restrict__ tickets,
                      const __grid_constant__ GemvEpilogue epi) {
     using Cfg = GemvCfg<W>;
     using T = GemvTmaCfg<W, OCC, MODE>;
     constexpr int C = Cfg::C;
     constexpr int kThreads = kGemvMaxWarps * 32;
+    // ONE: the instantiation for a single activation row (the ring's depth and strides are then constants).  It
+    // exists for the precisions where it measured faster (w = 4, 7, 8: +3 to +4 %; w = 5, 6 lost 4 to 5 %).
+    int M = ONE ? 1 : M_;
+    const int mpad = ONE ? 1 : mpad_;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // The table sits at the start of the dynamic area, so that its shared address is a constant.
     unsigned char* table = smem_raw;
@@ -618,10 +622,16 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         int most = 0;
         for (int mp = 1; mp <= 8; mp *= 2) most = T::total(mp) > most ? T::total(mp) : most;
-        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         if (e != cudaSuccess) return e;
+        if constexpr (W == 4 || W == 7 || W == 8) {
+            e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e != cudaSuccess) return e;
+            e = cudaFuncSetAttribute(gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e != cudaSuccess) return e;
+        }
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const int mpad = (M <= 1) ? 1 : (M <= 2) ? 2 : (M <= 4) ? 4 : 8;
@@ -635,10 +645,19 @@ static cudaError_t launch_tma_occ(const CUtensorMap& map, const __half* x, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    constexpr bool kOne = (W == 4 || W == 7 || W == 8);      // single-row instantiations: where they measured faster
+    if constexpr (kOne) {
+        if (M == 1 && splits <= 1)
+            return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false, true>, map, x, lut, out, M, N, K, mpad,
+                                      split_chunks, partials, tickets, epi);
+        if (M == 1)
+            return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true, true>, map, x, lut, out, M, N, K, mpad,
+                                      split_chunks, partials, tickets, epi);
+    }
     if (splits <= 1)                                         // no K split: the instantiation without that epilogue
-        return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false>, map, x, lut, out, M, N, K, mpad,
+        return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, false, false>, map, x, lut, out, M, N, K, mpad,
                                   split_chunks, partials, tickets, epi);
-    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true>, map, x, lut, out, M, N, K, mpad, split_chunks,
+    return cudaLaunchKernelEx(&cfg, gemv_kbit_tma_kernel<W, OCC, MODE, DEC, true, false>, map, x, lut, out, M, N, K, mpad, split_chunks,
                               partials, tickets, epi);
 }
 
