@@ -150,11 +150,34 @@ template <int W, int MODE = 0>
 __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint32_t (&wb)[W], const uint4 (&xv)[4],
                                              float (&acc)[2][4], const uint32_t (&lut_lo)[2][2],
                                              const uint32_t (&lut_hi)[2][2], uint32_t tab_a, uint32_t tab_b,
-                                             uint32_t tab_const = 0u, bool valid = true) {
+                                             uint32_t tab_const = 0u, bool valid = true, uint32_t pair_half = 0u) {
     // `valid` false (a word past the end of a short last group): the weights are taken as zero
     // without looking anything up, so that no table entry, finite or not, meets the (zeroed) activations.
     using Cfg = GemvCfg<W>;
-    if constexpr (MODE == 2) {
+    if constexpr (MODE == 3) {
+        // Compact pair tables: as mode 2, but an entry lives at index * 32 + g * 4 of its row set's table, i.e. the
+        // permuted (index << 8 | g * 32) shifted right by three.
+        uint32_t na[4], nb[4];
+        transpose_nibbles<W>(wa, na);
+        transpose_nibbles<W>(wb, nb);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t qa[4], qb[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                qa[c] = valid ? lds_u32(tab_const + (entry_offset_direct(na[c], 3 - j, tab_a) >> 3)) : 0u;
+                qb[c] = valid ? lds_u32(tab_const + pair_half + (entry_offset_direct(nb[c], 3 - j, tab_b) >> 3)) : 0u;
+            }
+            uint32_t xq[4];
+            xq[0] = __byte_perm(xv[j].w, xv[j].y, 0x7632);
+            xq[1] = __byte_perm(xv[j].w, xv[j].y, 0x5410);
+            xq[2] = __byte_perm(xv[j].z, xv[j].x, 0x7632);
+            xq[3] = __byte_perm(xv[j].z, xv[j].x, 0x5410);
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+                mma16816(acc[h], qa[2 * h], qb[2 * h], qa[2 * h + 1], qb[2 * h + 1], xq[2 * h], xq[2 * h + 1]);
+        }
+    } else if constexpr (MODE == 2) {
         // Pair tables: byte (3 - j) of na[c] / nb[c] is the index of the weight pair (e = 3 - c, e = 7 - c) of byte
         // group j.  One byte group at a time: eight lookups, four activation pairs, two MMAs, so that only eight
         // looked-up words are alive at once.

@@ -40,8 +40,8 @@ struct FalseType { static constexpr bool value = false; };
 // OCC: thread blocks per SM the kernel variant is built for (2 or 3).  Three blocks need a
 // register cap of 80, which costs instruction-level parallelism, and a smaller shared-memory
 // footprint; that pays only when a launch has more blocks than two per SM can hold at once.
-// MODE: 0, 1 or 2 as below; 2 is possible for w <= 4 only, and at w = 4 its 64 KB table leaves room
-// for the activations of at most two batch rows per chunk, so larger batches use mode 1 there.
+// MODE: 0 .. 3 as below; 2 and 3 are possible for w <= 4 only, and at w = 4 the 64 KB table of mode 2 leaves
+// room for the activations of at most two batch rows per chunk, so larger batches use mode 3 there.
 template <int W, int OCC, int MODE>
 struct GemvTmaCfg {
     // Table modes (see process_word):
@@ -52,11 +52,17 @@ struct GemvTmaCfg {
     //  1 (w = 5..7): one code's entries are spread over a 256-byte stripe (the lanes use the first
     //    128 bytes), so that a lookup address is a byte permute of the code word and nothing else.
     //  0 (w = 8): that table would be 64 KB; it keeps 128-byte stripes and a multiply-add per lookup.
+    //  3 (w = 3, 4): the pair table of mode 2 without a copy per lane: one 32-byte stripe per index holds the eight
+    //    rows g (a second table 8 KB further the rows g + 8): 16 KB at w = 4 instead of 64.  The four lanes of a row
+    //    now share four banks instead of owning one each (about two wavefronts per lookup) and an address costs a
+    //    shift more; it is for batches whose activations do not fit beside the 64 KB table.
     static constexpr int kMode = MODE;
-    static_assert(MODE == 0 || (MODE == 1 && W >= 4 && W <= 7) || (MODE == 2 && W <= 4), "table mode does not fit w_bits");
+    static_assert(MODE == 0 || (MODE == 1 && W >= 4 && W <= 7) || ((MODE == 2 || MODE == 3) && W <= 4), "table mode does not fit w_bits");
+    static constexpr int kPairHalf = (W == 4 ? 256 : 0x78) * 32;      // mode 3: bytes of the rows-g table
     static constexpr bool kDirect = kMode != 0;
     static constexpr int kEntryWords = kDirect ? 64 : 32;
     static constexpr int kTableBytes = kMode == 2 ? (W == 4 ? 65536 : 0x78 * 256)
+                                       : kMode == 3 ? 2 * kPairHalf
                                                   : (kMode == 1 ? GemvCfg<W>::C * 256 : GemvCfg<W>::kTableBytes);
     static constexpr int kPlaneBytes = W * 16 * 128;         // one box
     __host__ __device__ static constexpr int buffer_bytes(int mpad) {
@@ -285,7 +291,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     // Tables: w = 3 straight into registers, otherwise staged with ordinary cp.async (small).
     uint32_t lut_lo[2][2] = {{0u, 0u}, {0u, 0u}}, lut_hi[2][2] = {{0u, 0u}, {0u, 0u}};
     uint16_t* raw = reinterpret_cast<uint16_t*>(table);
-    if constexpr (Cfg::kRegLut && T::kMode != 2) {
+    if constexpr (Cfg::kRegLut && T::kMode != 2 && T::kMode != 3) {
 #pragma unroll
         for (int ab = 0; ab < 2; ab++) {
             const uint4 tv = __ldg(reinterpret_cast<const uint4*>(lut + (size_t)(row0 + g + 8 * ab) * C));
@@ -334,6 +340,34 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(dst + i * 4096), "r"(v) : "memory");
         }
         __syncthreads();
+    } else if constexpr (T::kMode == 3) {
+        // Compact pair table: entry (index = hi << 4 | lo, row r) = fp16 T[r][lo] in the low half, T[r][hi] in the
+        // high half, at index * 32 + (r & 7) * 4 of the table of its row set (rows 0..7, rows 8..15).
+        constexpr int kEntries = C * C * 16;
+        constexpr int kPerThread = (kEntries + kThreads - 1) / kThreads;
+        uint32_t val[kPerThread];
+        cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for (int n = 0; n < kPerThread; n++) {
+            const int e = tid + n * kThreads;
+            if (e < kEntries) {
+                const int r = e & 15, seq = e >> 4, lo = seq % C, hi = seq / C;
+                val[n] = (uint32_t)raw[r * Cfg::kRawStride + lo] | ((uint32_t)raw[r * Cfg::kRawStride + hi] << 16);
+            }
+        }
+        __syncthreads();                                     // the staged rows lie inside the table region
+        const uint32_t tab_sh = static_cast<uint32_t>(__cvta_generic_to_shared(table));
+#pragma unroll
+        for (int n = 0; n < kPerThread; n++) {
+            const int e = tid + n * kThreads;
+            if (e < kEntries) {
+                const int r = e & 15, seq = e >> 4, lo = seq % C, hi = seq / C;
+                const uint32_t dst = tab_sh + (r >> 3) * T::kPairHalf + ((hi << 4) | lo) * 32 + (r & 7) * 4;
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(val[n]) : "memory");
+            }
+        }
+        __syncthreads();
     } else if constexpr (!Cfg::kRegLut) {
         // Spread the staged rows into the [code][lane] table (the staging area lies inside the table
         // region).  An entry is (T[row g][code], T[row g + 8][code]); the four lanes t = 0..3 of a row
@@ -377,9 +411,9 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
     const uint32_t table_const = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
     uint32_t tab_a, tab_b;
     if constexpr (T::kDirect) {
-        tab_a = lane * 4;
+        tab_a = T::kMode == 3 ? (lane >> 2) * 32 : lane * 4;
         asm volatile("" : "+r"(tab_a)::"memory");
-        tab_b = tab_a + (T::kMode == 2 ? 128 : 2);
+        tab_b = T::kMode == 3 ? tab_a : tab_a + (T::kMode == 2 ? 128 : 2);
     } else {
         uint32_t table_sh = table_const;
         asm volatile("" : "+r"(table_sh)::"memory");
@@ -471,7 +505,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
                     // lab builds only: everything but the per-word arithmetic (loads, waits, hand-back, reduction)
                     acc[0][0] += __uint_as_float((wa[0] ^ wb[W - 1] ^ xv[0].x ^ xv[3].w) & 0x3fffffffu);
 #else
-                    process_word<W, T::kMode>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, table_const, valid_w);
+                    process_word<W, T::kMode>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, table_const, valid_w, T::kPairHalf);
 #endif
                 }
             };
@@ -677,8 +711,8 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
     splits = (chunks + split_chunks - 1) / split_chunks;
     *used = true;
     // Three blocks per SM (80 registers) only where two per SM could not hold the launch at once and
-    // the table leaves room for enough chunk buffers: measured, that is w = 3 (and w = 4 above two batch rows)
-    // from about 450 blocks on; everywhere else, w = 5 included, it loses.
+    // the table leaves room for enough chunk buffers: measured, that is w = 3 from about 450 blocks on;
+    // everywhere else (w = 5, and w = 4 with the compact pair table) it loses.
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -704,8 +738,7 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
         AP_TMA_GO(2, 2);
     } else if constexpr (W == 4) {
         if (M <= 2) AP_TMA_GO(2, 2);
-        if (many_blocks) AP_TMA_GO(3, 1);
-        AP_TMA_GO(2, 1);
+        AP_TMA_GO(2, 3);                                     // more rows: the compact pair table (8 % faster than mode 1)
     } else if constexpr (W <= 7) {
         AP_TMA_GO(2, 1);
     } else {
