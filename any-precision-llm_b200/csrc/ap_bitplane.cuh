@@ -81,6 +81,30 @@ __device__ __forceinline__ void transpose_nibbles(const uint32_t (&planes)[W], u
     for (int c = 0; c < 4; c++) nb[c] = r[c];
 }
 
+// For W <= 4, pairs of NEIGHBOURING weights: the plane index is exchanged with bits 2 and 1 of the bit position
+// instead of bits 1 and 0.  On return pr[c], c = 0..3, holds in byte (3 - j) the codes of the weights e = 6 - 2c
+// and e = 7 - 2c of byte group j, interleaved bit by bit: bit 2i + 1 of the byte is bit i of the code of the even
+// weight (e = 6 - 2c), bit 2i that of the odd weight (e = 7 - 2c).  The byte is the index of that pair into a
+// table of pairs, and the pair's activations are one 32-bit word of the activation row as it lies in memory.
+template <int W>
+__device__ __forceinline__ void transpose_pairs(const uint32_t (&planes)[W], uint32_t (&pr)[4]) {
+    static_assert(W <= 4, "pair codes need W <= 4");
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) r[i] = (i < W) ? planes[W - 1 - i] : 0u;
+    swap_blocks<4>(r[0], r[2]);
+    swap_blocks<4>(r[1], r[3]);
+    swap_blocks<2>(r[0], r[1]);
+    swap_blocks<2>(r[2], r[3]);
+#pragma unroll
+    for (int c = 0; c < 4; c++) pr[c] = r[c];
+}
+
+// Bit i of v moved to bit 2i (v below 16): the place of one code's bits inside the index byte of transpose_pairs.
+__host__ __device__ constexpr uint32_t spread_bits(uint32_t v) {
+    return (v & 1u) | ((v & 2u) << 1) | ((v & 4u) << 2) | ((v & 8u) << 3);
+}
+
 // Geometry of a row for kernels that read 16-byte vectors (4 consecutive words) of a
 // row-plane.  Requires K % 128 == 0 so that rows and the partial group are whole vectors.
 struct RowGeom {

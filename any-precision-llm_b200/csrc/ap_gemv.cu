@@ -143,9 +143,19 @@ struct GemvCfg {
 //         stripes at address tab_a / tab_b (one multiply-add per lookup).
 // MODE 1: the table has 256-byte code stripes at the constant shared address tab_const, and
 //         tab_a / tab_b are the lane's byte offsets inside a stripe instead of addresses.
-// MODE 2: w <= 4; the table is indexed by the codes of TWO weights (a byte of the nibble
-//         transpose) and an entry is the fp16 pair itself: one 32-bit load per two weights and no
-//         packing.  Stripes and tab_const / tab_a / tab_b as in MODE 1.
+// MODE 2: w <= 4; the table is indexed by the codes of TWO weights and an entry is the fp16 pair itself: one
+//         32-bit load per two weights and no packing.  Stripes and tab_const / tab_a / tab_b as in MODE 1.
+//         Which two weights: see kNeighbourPairs.
+// MODE 3: the pair table without a copy per lane (32-byte stripes; tab_const + pair_half is the rows g + 8's table).
+// Pairs of neighbouring weights (transpose_pairs: the index byte interleaves the two codes, the activations are
+// used as loaded, and at w = 3 the table has 64 stripes) or the two nibbles of a byte of transpose_nibbles (weights
+// e and e + 4; the activations are re-paired with four permutes per byte group).  Measured per shape on a B200:
+// neighbours win at w = 3 (same time for one row, 17 % faster for eight rows on launches of many blocks, whose table
+// halves) and with the compact table of mode 3 (3 %); at w = 4 with the full table they lose 1 % over the
+// Llama-2-7B layer set (11008 x 4096: 11.9 -> 12.3 us), so that case keeps the nibbles.
+template <int W, int MODE>
+constexpr bool kNeighbourPairs = (MODE == 3) || (MODE == 2 && W == 3);
+
 template <int W, int MODE = 0>
 __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint32_t (&wb)[W], const uint4 (&xv)[4],
                                              float (&acc)[2][4], const uint32_t (&lut_lo)[2][2],
@@ -158,8 +168,8 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
         // Compact pair tables: as mode 2, but an entry lives at index * 32 + g * 4 of its row set's table, i.e. the
         // permuted (index << 8 | g * 32) shifted right by three.
         uint32_t na[4], nb[4];
-        transpose_nibbles<W>(wa, na);
-        transpose_nibbles<W>(wb, nb);
+        transpose_pairs<W>(wa, na);
+        transpose_pairs<W>(wb, nb);
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             uint32_t qa[4], qb[4];
@@ -168,39 +178,44 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
                 qa[c] = valid ? lds_u32(tab_const + (entry_offset_direct(na[c], 3 - j, tab_a) >> 3)) : 0u;
                 qb[c] = valid ? lds_u32(tab_const + pair_half + (entry_offset_direct(nb[c], 3 - j, tab_b) >> 3)) : 0u;
             }
-            uint32_t xq[4];
-            xq[0] = __byte_perm(xv[j].w, xv[j].y, 0x7632);
-            xq[1] = __byte_perm(xv[j].w, xv[j].y, 0x5410);
-            xq[2] = __byte_perm(xv[j].z, xv[j].x, 0x7632);
-            xq[3] = __byte_perm(xv[j].z, xv[j].x, 0x5410);
-#pragma unroll
-            for (int h = 0; h < 2; h++)
-                mma16816(acc[h], qa[2 * h], qb[2 * h], qa[2 * h + 1], qb[2 * h + 1], xq[2 * h], xq[2 * h + 1]);
+            mma16816(acc[0], qa[0], qb[0], qa[1], qb[1], xv[j].w, xv[j].z);
+            mma16816(acc[1], qa[2], qb[2], qa[3], qb[3], xv[j].y, xv[j].x);
         }
     } else if constexpr (MODE == 2) {
-        // Pair tables: byte (3 - j) of na[c] / nb[c] is the index of the weight pair (e = 3 - c, e = 7 - c) of byte
-        // group j.  One byte group at a time: eight lookups, four activation pairs, two MMAs, so that only eight
-        // looked-up words are alive at once.
+        // Pair tables: byte (3 - j) of na[c] / nb[c] is the index of a weight pair of byte group j: the neighbours
+        // (e = 6 - 2c, e = 7 - 2c), or (e = 3 - c, e = 7 - c) with the nibble transpose.  One byte group at a time:
+        // eight lookups and two MMAs, so that only eight looked-up words are alive at once.
         uint32_t na[4], nb[4];
-        transpose_nibbles<W>(wa, na);
-        transpose_nibbles<W>(wb, nb);
+        if constexpr (kNeighbourPairs<W, MODE>) {
+            transpose_pairs<W>(wa, na);
+            transpose_pairs<W>(wb, nb);
+        } else {
+            transpose_nibbles<W>(wa, na);
+            transpose_nibbles<W>(wb, nb);
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            uint32_t qa[4], qb[4];                           // fp16x2 (W[e = 7-c], W[e = 3-c]) of rows g and g + 8
+            uint32_t qa[4], qb[4];                           // fp16x2 weight pairs of rows g and g + 8
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 qa[c] = valid ? lds_u32(tab_const + entry_offset_direct(na[c], 3 - j, tab_a)) : 0u;
                 qb[c] = valid ? lds_u32(tab_const + entry_offset_direct(nb[c], 3 - j, tab_b)) : 0u;
             }
-            // activations paired the same way: xq[c] = (x[7-c], x[3-c])
-            uint32_t xq[4];
-            xq[0] = __byte_perm(xv[j].w, xv[j].y, 0x7632);
-            xq[1] = __byte_perm(xv[j].w, xv[j].y, 0x5410);
-            xq[2] = __byte_perm(xv[j].z, xv[j].x, 0x7632);
-            xq[3] = __byte_perm(xv[j].z, xv[j].x, 0x5410);
+            if constexpr (kNeighbourPairs<W, MODE>) {
+                // the pair's activations (x[6-2c], x[7-2c]) are a word of the row as it was loaded
+                mma16816(acc[0], qa[0], qb[0], qa[1], qb[1], xv[j].w, xv[j].z);
+                mma16816(acc[1], qa[2], qb[2], qa[3], qb[3], xv[j].y, xv[j].x);
+            } else {
+                // activations paired like the weights: xq[c] = (x[7-c], x[3-c])
+                uint32_t xq[4];
+                xq[0] = __byte_perm(xv[j].w, xv[j].y, 0x7632);
+                xq[1] = __byte_perm(xv[j].w, xv[j].y, 0x5410);
+                xq[2] = __byte_perm(xv[j].z, xv[j].x, 0x7632);
+                xq[3] = __byte_perm(xv[j].z, xv[j].x, 0x5410);
 #pragma unroll
-            for (int h = 0; h < 2; h++)
-                mma16816(acc[h], qa[2 * h], qb[2 * h], qa[2 * h + 1], qb[2 * h + 1], xq[2 * h], xq[2 * h + 1]);
+                for (int h = 0; h < 2; h++)
+                    mma16816(acc[h], qa[2 * h], qb[2 * h], qa[2 * h + 1], qb[2 * h + 1], xq[2 * h], xq[2 * h + 1]);
+            }
         }
     } else if constexpr (Cfg::kRegLut) {
         // w = 3 without pair tables: the row's eight table entries live in four registers and a byte permute with

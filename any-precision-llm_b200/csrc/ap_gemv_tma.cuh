@@ -45,10 +45,10 @@ struct FalseType { static constexpr bool value = false; };
 template <int W, int OCC, int MODE>
 struct GemvTmaCfg {
     // Table modes (see process_word):
-    //  2 (w = 3, 4): indexed by the codes of two weights (one byte of the nibble transpose); a
-    //    256-byte stripe per index holds the fp16 pair of the lane's row g (bytes 0..127, lane * 4)
-    //    and of its row g + 8 (bytes 128..255).  256 stripes at w = 4 (64 KB); at w = 3 the index has
-    //    two bits that are always zero, the stripes in use are scattered over 0x78 of them (30 KB).
+    //  2 (w = 3, 4): indexed by the codes of two weights (see kNeighbourPairs: one byte of transpose_nibbles at
+    //    w = 4, of transpose_pairs at w = 3); a 256-byte stripe per index holds the fp16 pair of the lane's row g
+    //    (bytes 0..127, lane * 4) and of its row g + 8 (bytes 128..255).  256 stripes at w = 4 (64 KB), 64 at
+    //    w = 3 (16 KB).
     //  1 (w = 5..7): one code's entries are spread over a 256-byte stripe (the lanes use the first
     //    128 bytes), so that a lookup address is a byte permute of the code word and nothing else.
     //  0 (w = 8): that table would be 64 KB; it keeps 128-byte stripes and a multiply-add per lookup.
@@ -58,10 +58,10 @@ struct GemvTmaCfg {
     //    shift more; it is for batches whose activations do not fit beside the 64 KB table.
     static constexpr int kMode = MODE;
     static_assert(MODE == 0 || (MODE == 1 && W >= 4 && W <= 7) || ((MODE == 2 || MODE == 3) && W <= 4), "table mode does not fit w_bits");
-    static constexpr int kPairHalf = (W == 4 ? 256 : 0x78) * 32;      // mode 3: bytes of the rows-g table
+    static constexpr int kPairHalf = (W == 4 ? 256 : 64) * 32;        // mode 3: bytes of the rows-g table
     static constexpr bool kDirect = kMode != 0;
     static constexpr int kEntryWords = kDirect ? 64 : 32;
-    static constexpr int kTableBytes = kMode == 2 ? (W == 4 ? 65536 : 0x78 * 256)
+    static constexpr int kTableBytes = kMode == 2 ? (W == 4 ? 65536 : 64 * 256)
                                        : kMode == 3 ? 2 * kPairHalf
                                                   : (kMode == 1 ? GemvCfg<W>::C * 256 : GemvCfg<W>::kTableBytes);
     static constexpr int kPlaneBytes = W * 16 * 128;         // one box
@@ -333,37 +333,43 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
 #pragma unroll
         for (int i = 0; i < kHi / 2; i++) thi[i] = *reinterpret_cast<const uint32_t*>(row + hi0 + 2 * i);
         __syncthreads();                                     // the staged rows lie inside the table region
-        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(table)) + lo * 256 + hi0 * 4096 + half * 128 + bg * 16;
+        // index byte: hi << 4 | lo for the nibble pairs; for neighbouring pairs the bits of the low half's code at
+        // the odd places and those of the high half's at the even ones
+        constexpr bool kNb = kNeighbourPairs<W, MODE>;
+        const uint32_t first = kNb ? ((spread_bits((uint32_t)lo) << 1) | spread_bits((uint32_t)hi0)) : (uint32_t)(lo + 16 * hi0);
+        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(table)) + first * 256 + half * 128 + bg * 16;
 #pragma unroll
         for (int i = 0; i < kHi; i++) {
             const uint32_t v = __byte_perm(tlo, thi[i >> 1], (i & 1) ? 0x7610u : 0x5410u);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(dst + i * 4096), "r"(v) : "memory");
+            const uint32_t step = (kNb ? spread_bits((uint32_t)i) : 16u * (uint32_t)i) * 256u;
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(dst + step), "r"(v) : "memory");
         }
         __syncthreads();
     } else if constexpr (T::kMode == 3) {
-        // Compact pair table: entry (index = hi << 4 | lo, row r) = fp16 T[r][lo] in the low half, T[r][hi] in the
-        // high half, at index * 32 + (r & 7) * 4 of the table of its row set (rows 0..7, rows 8..15).
+        // Compact pair table: entry (lo, hi, row r) = fp16 T[r][lo] in the low half, T[r][hi] in the high half, at
+        // index * 32 + (r & 7) * 4 of the table of its row set (rows 0..7, rows 8..15); the index has the bits of lo
+        // at its odd places and those of hi at its even places (transpose_pairs).  Thread tid serves row tid & 15
+        // and the pairs number (tid >> 4) + 16 n: with 16 codes lo is fixed per thread and hi = n.
+        static_assert(kThreads == 256, "the pair numbering below assumes 256 threads");
         constexpr int kEntries = C * C * 16;
         constexpr int kPerThread = (kEntries + kThreads - 1) / kThreads;
         uint32_t val[kPerThread];
         cp_async_wait<0>();
         __syncthreads();
+        const int r = tid & 15, t4 = tid >> 4;
 #pragma unroll
         for (int n = 0; n < kPerThread; n++) {
-            const int e = tid + n * kThreads;
-            if (e < kEntries) {
-                const int r = e & 15, seq = e >> 4, lo = seq % C, hi = seq / C;
+            const int lo = (C == 16) ? t4 : (t4 + 16 * n) % C, hi = (C == 16) ? n : (t4 + 16 * n) / C;
+            if (C == 16 || hi < C)
                 val[n] = (uint32_t)raw[r * Cfg::kRawStride + lo] | ((uint32_t)raw[r * Cfg::kRawStride + hi] << 16);
-            }
         }
         __syncthreads();                                     // the staged rows lie inside the table region
-        const uint32_t tab_sh = static_cast<uint32_t>(__cvta_generic_to_shared(table));
+        const uint32_t tab_sh = static_cast<uint32_t>(__cvta_generic_to_shared(table)) + (r >> 3) * T::kPairHalf + (r & 7) * 4;
 #pragma unroll
         for (int n = 0; n < kPerThread; n++) {
-            const int e = tid + n * kThreads;
-            if (e < kEntries) {
-                const int r = e & 15, seq = e >> 4, lo = seq % C, hi = seq / C;
-                const uint32_t dst = tab_sh + (r >> 3) * T::kPairHalf + ((hi << 4) | lo) * 32 + (r & 7) * 4;
+            const int lo = (C == 16) ? t4 : (t4 + 16 * n) % C, hi = (C == 16) ? n : (t4 + 16 * n) / C;
+            if (C == 16 || hi < C) {
+                const uint32_t dst = tab_sh + ((spread_bits((uint32_t)lo) << 1) | spread_bits((uint32_t)hi)) * 32;
                 asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(val[n]) : "memory");
             }
         }
