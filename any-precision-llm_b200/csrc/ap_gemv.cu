@@ -178,8 +178,8 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
                 qa[c] = valid ? lds_u32(tab_const + (entry_offset_direct(na[c], 3 - j, tab_a) >> 3)) : 0u;
                 qb[c] = valid ? lds_u32(tab_const + pair_half + (entry_offset_direct(nb[c], 3 - j, tab_b) >> 3)) : 0u;
             }
-            mma16816(acc[0], qa[0], qb[0], qa[1], qb[1], xv[j].w, xv[j].z);
-            mma16816(acc[1], qa[2], qb[2], qa[3], qb[3], xv[j].y, xv[j].x);
+            mma16816(acc[0], qa[1], qb[1], qa[0], qb[0], xv[j].z, xv[j].w);
+            mma16816(acc[1], qa[3], qb[3], qa[2], qb[2], xv[j].x, xv[j].y);
         }
     } else if constexpr (MODE == 2) {
         // Pair tables: byte (3 - j) of na[c] / nb[c] is the index of a weight pair of byte group j: the neighbours
@@ -202,9 +202,10 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
                 qb[c] = valid ? lds_u32(tab_const + entry_offset_direct(nb[c], 3 - j, tab_b)) : 0u;
             }
             if constexpr (kNeighbourPairs<W, MODE>) {
-                // the pair's activations (x[6-2c], x[7-2c]) are a word of the row as it was loaded
-                mma16816(acc[0], qa[0], qb[0], qa[1], qb[1], xv[j].w, xv[j].z);
-                mma16816(acc[1], qa[2], qb[2], qa[3], qb[3], xv[j].y, xv[j].x);
+                // the pair's activations (x[6-2c], x[7-2c]) are a word of the row as it was loaded; the two words of
+                // an MMA in the order they were loaded in, which is the register pair the instruction wants
+                mma16816(acc[0], qa[1], qb[1], qa[0], qb[0], xv[j].z, xv[j].w);
+                mma16816(acc[1], qa[3], qb[3], qa[2], qb[2], xv[j].x, xv[j].y);
             } else {
                 // activations paired like the weights: xq[c] = (x[7-c], x[3-c])
                 uint32_t xq[4];
