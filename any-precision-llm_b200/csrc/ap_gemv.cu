@@ -150,9 +150,10 @@ struct GemvCfg {
 // Pairs of neighbouring weights (transpose_pairs: the index byte interleaves the two codes, the activations are
 // used as loaded, and at w = 3 the table has 64 stripes) or the two nibbles of a byte of transpose_nibbles (weights
 // e and e + 4; the activations are re-paired with four permutes per byte group).  Measured per shape on a B200:
-// neighbours win at w = 3 (same time for one row, 17 % faster for eight rows on launches of many blocks, whose table
-// halves) and with the compact table of mode 3 (3 %); at w = 4 with the full table they lose 1 % over the
-// Llama-2-7B layer set (11008 x 4096: 11.9 -> 12.3 us), so that case keeps the nibbles.
+// neighbours win at w = 3 (2 % for one row, 20 % for eight rows on launches of many blocks, whose table halves)
+// and with the compact table of mode 3 (up to 3 %); at w = 4 with the full table they win 3-4 % on 4096 x 4096
+// and 4096 x 11008 but lose 3 % on 11008 x 4096 (11.9 -> 12.3 us), nothing over the Llama-2-7B layer set, so
+// that case keeps the nibbles.
 template <int W, int MODE>
 constexpr bool kNeighbourPairs = (MODE == 3) || (MODE == 2 && W == 3);
 
