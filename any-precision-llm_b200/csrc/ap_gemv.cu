@@ -152,12 +152,12 @@ struct GemvCfg {
 // e and e + 4; the activations are re-paired with four permutes per byte group).  Measured per shape on a B200:
 // neighbours win at w = 3 (2 % for one row, 20 % for eight rows on launches of many blocks, whose table halves)
 // and with the compact table of mode 3 (up to 3 %); at w = 4 with the full table they win 3-4 % on 4096 x 4096
-// and 4096 x 11008 but lose 3 % on 11008 x 4096 (11.9 -> 12.3 us), nothing over the Llama-2-7B layer set, so
-// that case keeps the nibbles.
+// and 4096 x 11008 but lose 3 % on 11008 x 4096 (11.9 -> 12.3 us), so that case has both (NB chosen per launch:
+// nibbles for launches of many blocks).
 template <int W, int MODE>
 constexpr bool kNeighbourPairs = (MODE == 3) || (MODE == 2 && W == 3);
 
-template <int W, int MODE = 0>
+template <int W, int MODE = 0, bool NB = kNeighbourPairs<W, MODE>>
 __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint32_t (&wb)[W], const uint4 (&xv)[4],
                                              float (&acc)[2][4], const uint32_t (&lut_lo)[2][2],
                                              const uint32_t (&lut_hi)[2][2], uint32_t tab_a, uint32_t tab_b,
@@ -187,7 +187,7 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
         // (e = 6 - 2c, e = 7 - 2c), or (e = 3 - c, e = 7 - c) with the nibble transpose.  One byte group at a time:
         // eight lookups and two MMAs, so that only eight looked-up words are alive at once.
         uint32_t na[4], nb[4];
-        if constexpr (kNeighbourPairs<W, MODE>) {
+        if constexpr (NB) {
             transpose_pairs<W>(wa, na);
             transpose_pairs<W>(wb, nb);
         } else {
@@ -202,7 +202,7 @@ __device__ __forceinline__ void process_word(const uint32_t (&wa)[W], const uint
                 qa[c] = valid ? lds_u32(tab_const + entry_offset_direct(na[c], 3 - j, tab_a)) : 0u;
                 qb[c] = valid ? lds_u32(tab_const + entry_offset_direct(nb[c], 3 - j, tab_b)) : 0u;
             }
-            if constexpr (kNeighbourPairs<W, MODE>) {
+            if constexpr (NB) {
                 // the pair's activations (x[6-2c], x[7-2c]) are a word of the row as it was loaded; the two words of
                 // an MMA in the order they were loaded in, which is the register pair the instruction wants
                 mma16816(acc[0], qa[1], qb[1], qa[0], qb[0], xv[j].z, xv[j].w);

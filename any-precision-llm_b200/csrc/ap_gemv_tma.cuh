@@ -40,8 +40,8 @@ struct FalseType { static constexpr bool value = false; };
 // OCC: thread blocks per SM the kernel variant is built for (2 or 3).  Three blocks need a
 // register cap of 80, which costs instruction-level parallelism, and a smaller shared-memory
 // footprint; that pays only when a launch has more blocks than two per SM can hold at once.
-// MODE: 0 .. 3 as below; 2 and 3 are possible for w <= 4 only, and at w = 4 the 64 KB table of mode 2 leaves
-// room for the activations of at most two batch rows per chunk, so larger batches use mode 3 there.
+// MODE: 0 .. 3 and 5 as below; 2, 3 and 5 are possible for w <= 4 only, and at w = 4 the 64 KB table of modes 2 and 5
+// leaves room for the activations of at most two batch rows per chunk, so larger batches use mode 3 there.
 template <int W, int OCC, int MODE>
 struct GemvTmaCfg {
     // Table modes (see process_word):
@@ -56,8 +56,11 @@ struct GemvTmaCfg {
     //    rows g (a second table 8 KB further the rows g + 8): 16 KB at w = 4 instead of 64.  The four lanes of a row
     //    now share four banks instead of owning one each (about two wavefronts per lookup) and an address costs a
     //    shift more; it is for batches whose activations do not fit beside the 64 KB table.
-    static constexpr int kMode = MODE;
-    static_assert(MODE == 0 || (MODE == 1 && W >= 4 && W <= 7) || ((MODE == 2 || MODE == 3) && W <= 4), "table mode does not fit w_bits");
+    //  5 (w = 4): mode 2 with pairs of neighbouring weights (kNb) instead of the nibble pairs.
+    static constexpr int kMode = MODE == 5 ? 2 : MODE;
+    static constexpr bool kNb = MODE == 5 || kNeighbourPairs<W, MODE>;
+    static_assert(MODE == 0 || (MODE == 1 && W >= 4 && W <= 7) || ((MODE == 2 || MODE == 3) && W <= 4) || (MODE == 5 && W == 4),
+                  "table mode does not fit w_bits");
     static constexpr int kPairHalf = (W == 4 ? 256 : 64) * 32;        // mode 3: bytes of the rows-g table
     static constexpr bool kDirect = kMode != 0;
     static constexpr int kEntryWords = kDirect ? 64 : 32;
@@ -335,7 +338,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
         __syncthreads();                                     // the staged rows lie inside the table region
         // index byte: hi << 4 | lo for the nibble pairs; for neighbouring pairs the bits of the low half's code at
         // the odd places and those of the high half's at the even ones
-        constexpr bool kNb = kNeighbourPairs<W, MODE>;
+        constexpr bool kNb = T::kNb;
         const uint32_t first = kNb ? ((spread_bits((uint32_t)lo) << 1) | spread_bits((uint32_t)hi0)) : (uint32_t)(lo + 16 * hi0);
         const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(table)) + first * 256 + half * 128 + bg * 16;
 #pragma unroll
@@ -511,7 +514,7 @@ gemv_kbit_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __half* __r
                     // lab builds only: everything but the per-word arithmetic (loads, waits, hand-back, reduction)
                     acc[0][0] += __uint_as_float((wa[0] ^ wb[W - 1] ^ xv[0].x ^ xv[3].w) & 0x3fffffffu);
 #else
-                    process_word<W, T::kMode>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, table_const, valid_w, T::kPairHalf);
+                    process_word<W, T::kMode, T::kNb>(wa, wb, xv, acc, lut_lo, lut_hi, tab_a, tab_b, table_const, valid_w, T::kPairHalf);
 #endif
                 }
             };
@@ -743,7 +746,8 @@ static cudaError_t launch_tma(const __half* x, const uint32_t* q, long long plan
         if (many_blocks) AP_TMA_GO(3, 2);
         AP_TMA_GO(2, 2);
     } else if constexpr (W == 4) {
-        if (M <= 2) AP_TMA_GO(2, 2);
+        if (M <= 2 && many_blocks) AP_TMA_GO(2, 2);          // nibble pairs (3 % faster than neighbours on 11008 x 4096)
+        if (M <= 2) AP_TMA_GO(2, 5);                         // neighbouring pairs (3-4 % faster on 4096 x 4096, 4096 x 11008)
         AP_TMA_GO(2, 3);                                     // more rows: the compact pair table (8 % faster than mode 1)
     } else if constexpr (W <= 7) {
         AP_TMA_GO(2, 1);
